@@ -15,7 +15,12 @@
 //
 // rope_store: optionally each query and key head divided by its root mean square and multiplied by a gain
 // per dimension (shared by the heads), then rotary encoding of the first rot_dim dimensions of every query
-// and key head (dimension i is paired with i + rot_dim/2), cache write of keys and values.
+// and key head (dimension i is paired with i + rot_dim/2, or, `neighbours`, dimension 2i with 2i + 1), cache
+// write of keys and values.  With `v_first` a token's values are first blended with another layer's values of
+// the same token, v <- (1 - lam) v + lam v_first (float rows of their own stride; lam one float on the device).
+//
+// `sink`: the softmax counts one key more, of score 0 and without a value: p_j = exp(s_j) / (1 + sum exp(s_j)).
+// The running maximum then starts at 0 and the running sum at 1 instead of at -inf and 0.
 
 #include "common.cuh"
 
@@ -27,7 +32,8 @@ __global__ void __launch_bounds__(256)
 rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                   const int* __restrict__ slot_mapping, AT* __restrict__ q_out, AT* __restrict__ k_cache,
                   AT* __restrict__ v_cache, int nh, int nkv, int dk, int dv, int rot_dim, int page_size,
-                  const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps) {
+                  const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps, int neighbours,
+                  const float* __restrict__ v_first, int64_t v_first_stride, const float* __restrict__ lam_ptr) {
     extern __shared__ float trig[];                 // cos and sin of this token's rot_dim / 2 angles
     float* inv_rms = trig + (rot_dim > 0 ? rot_dim : 1);    // [nh + nkv], with head norms only
     wait_for_earlier_kernels();
@@ -62,12 +68,14 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
         const float* gain = head < nh ? q_gain : k_gain;
         if (normed) v = v * inv_rms[head] * gain[c];
         if (c < rot_dim) {
-            const int i = c < half ? c : c - half;
+            // the first of a pair becomes u cos - v sin, the second v cos + u sin
+            const bool first = neighbours ? !(c & 1) : c < half;
+            const int i = neighbours ? c >> 1 : (c < half ? c : c - half);
             const float cs = trig[i], sn = trig[half + i];
-            const int co = c < half ? c + half : c - half;
+            const int co = neighbours ? (c ^ 1) : (c < half ? c + half : c - half);
             float other = row[head * dk + co];
             if (normed) other = other * inv_rms[head] * gain[co];
-            v = c < half ? v * cs - other * sn : v * cs + other * sn;
+            v = first ? v * cs - other * sn : v * cs + other * sn;
         }
         if (head < nh) {
             q_out[(int64_t)t * nh * dk + idx] = from_float<AT>(v);
@@ -79,9 +87,12 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
     }
     if (slot >= 0) {
         const int page = slot / page_size, off = slot - page * page_size;
+        const float lam = v_first ? lam_ptr[0] : 0.f;
         for (int idx = threadIdx.x; idx < nkv * dv; idx += blockDim.x) {
             const int hk = idx / dv, c = idx - hk * dv;
-            v_cache[(((int64_t)page * nkv + hk) * page_size + off) * dv + c] = from_float<AT>(row[nqk + idx]);
+            float v = row[nqk + idx];
+            if (v_first) v = (1.0f - lam) * v + lam * v_first[(int64_t)t * v_first_stride + idx];
+            v_cache[(((int64_t)page * nkv + hk) * page_size + off) * dv + c] = from_float<AT>(v);
         }
     }
 }
@@ -102,7 +113,8 @@ __global__ void __launch_bounds__(256)
 attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const AT* __restrict__ v_cache,
                 const float* __restrict__ mix, const int* __restrict__ block_table, const int* __restrict__ q_start,
                 const int* __restrict__ kv_len, AT* __restrict__ out, int H, int G, int dk, int dv, int page_size,
-                int max_pages, int window, float scale, float cap, int QT, int KT, int rpw, int keep_first, int vrs) {
+                int max_pages, int window, float scale, float cap, int QT, int KT, int rpw, int keep_first, int vrs,
+                int sink) {
     constexpr int RPW = MixCfg<AT, CPL>::RPW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     wait_for_earlier_kernels();
@@ -141,7 +153,7 @@ attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const 
     int g_of[RPW];
 #pragma unroll
     for (int m = 0; m < RPW; ++m) {
-        m_run[m] = -INFINITY; l_run[m] = 0.f;
+        m_run[m] = sink ? 0.f : -INFINITY; l_run[m] = sink ? 1.f : 0.f;
         const int r = warp * rpw + m;
         g_of[m] = (r < R ? r / QT : 0) / rep;
 #pragma unroll
@@ -338,8 +350,8 @@ extern "C" {
 
 int mi_rope_store(const float* qkv, const int* positions, const float* inv_freq, const int* slot_mapping,
                   void* q_out, void* k_cache, void* v_cache, int adtype, int T, int nh, int nkv, int dk, int dv,
-                  int rot_dim, int page_size, const float* q_gain, const float* k_gain, float eps,
-                  cudaStream_t stream) {
+                  int rot_dim, int page_size, const float* q_gain, const float* k_gain, float eps, int neighbours,
+                  const float* v_first, int64_t v_first_stride, const float* lam, cudaStream_t stream) {
     if (T <= 0) return kOk;
     if ((q_gain == nullptr) != (k_gain == nullptr)) {
         set_last_error("rope_store: the gains of the query norm and of the key norm come together");
@@ -349,11 +361,15 @@ int mi_rope_store(const float* qkv, const int* positions, const float* inv_freq,
         set_last_error("rope_store: %d rotary dimensions of a head of %d", rot_dim, dk);
         return kBadShape;
     }
+    if (v_first && (!lam || v_first_stride < (int64_t)nkv * dv)) {
+        set_last_error("rope_store: blended values need their weight and rows of at least %d", nkv * dv);
+        return kBadShape;
+    }
     MI_DISPATCH_1(adtype, AT,
         launch_dependent(rope_store_kernel<AT>, dim3(T), dim3(256),
                          sizeof(float) * ((rot_dim > 0 ? rot_dim : 1) + nh + nkv), stream, qkv, positions, inv_freq,
                          slot_mapping, (AT*)q_out, (AT*)k_cache, (AT*)v_cache, nh, nkv, dk, dv, rot_dim, page_size,
-                         q_gain, k_gain, eps));
+                         q_gain, k_gain, eps, neighbours, v_first, v_first_stride, lam));
     return finish_launch("rope_store");
 }
 
@@ -366,7 +382,7 @@ int mi_attn_mix_supported(int H, int G, int dk, int dv, int esize) {
 int mi_attn_mix(const void* q, const void* k_cache, const void* v_cache, int adtype, const float* mix,
                 const int* block_table, const int* q_start, const int* kv_len, void* out, int B, int max_q_len,
                 int H, int G, int dk, int dv, int page_size, int max_pages, int window, float scale, float cap,
-                int keep_first, int vrs, cudaStream_t stream) {
+                int keep_first, int vrs, int sink, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return kOk;
     if (keep_first < 0 || vrs < dv) {
         set_last_error("mixed-head attention: %d kept first keys, value rows of %d every %d elements", keep_first, dv, vrs);
@@ -392,7 +408,7 @@ int mi_attn_mix(const void* q, const void* k_cache, const void* v_cache, int adt
         launch_dependent(attn_mix_kernel<AT, CPL>, grid, dim3(256), p.smem, stream, (const AT*)q,            \
                          (const AT*)k_cache, (const AT*)v_cache, mix, block_table, q_start, kv_len, (AT*)out, \
                          H, G, dk, dv, page_size, max_pages, window, scale, cap, p.QT, p.KT, p.rpw,          \
-                         keep_first, vrs);                                                                    \
+                         keep_first, vrs, sink);                                                              \
     })
     if (cpl <= 1) MI_MIX_LAUNCH(1);
     else if (cpl <= 2) MI_MIX_LAUNCH(2);

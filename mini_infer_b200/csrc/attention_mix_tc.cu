@@ -57,7 +57,7 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ block_table, const int* __restrict__ q_start,
                    const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int H, int G, int dk, int page_size, int max_pages, int window,
-                   float scale, float cap, int splits, int hgroups, int keep_first, int vrs) {
+                   float scale, float cap, int splits, int hgroups, int keep_first, int vrs, int sink) {
     constexpr int DV = NT * 8;
     constexpr int SP = KT + 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -101,8 +101,11 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     float m_run[HPW][2], l_run[HPW][2];
 #pragma unroll
     for (int hh = 0; hh < HPW; ++hh) {
-        m_run[hh][0] = m_run[hh][1] = -INFINITY;
-        l_run[hh][0] = l_run[hh][1] = 0.f;
+        // a key more of score 0 and no value (`sink`): of an unsplit step the running maximum starts at 0 and
+        // the running sum at 1 (in one lane of the quad that shares a row); a split step leaves it to the merge
+        const bool sunk = sink && splits == 1;
+        m_run[hh][0] = m_run[hh][1] = sunk ? 0.f : -INFINITY;
+        l_run[hh][0] = l_run[hh][1] = (sunk && (lane & 3) == 0) ? 1.f : 0.f;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -362,7 +365,8 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 constexpr int kMergeMaxSplits = 12288;          // two floats a split in shared memory: 96 KiB
 __global__ void __launch_bounds__(128)
 attn_mix_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                      const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, int H, int DV, int splits) {
+                      const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, int H, int DV, int splits,
+                      int sink) {
     extern __shared__ float merge_sh[];         // [splits] weights, [splits] sums
     float* wgt = merge_sh;
     float* lsum = merge_sh + splits;
@@ -374,12 +378,12 @@ attn_mix_merge_kernel(const float* __restrict__ part_o, const float* __restrict_
         lsum[s] = ml.y;
     }
     __syncthreads();
-    float m = -INFINITY;
+    float m = sink ? 0.f : -INFINITY;           // the key of score 0 that `sink` adds counts here, once
     for (int s = 0; s < splits; ++s) m = fmaxf(m, wgt[s]);
     __syncthreads();
     for (int s = threadIdx.x; s < splits; s += blockDim.x) wgt[s] = wgt[s] == -INFINITY ? 0.f : expf(wgt[s] - m);
     __syncthreads();
-    float l = 0.f;
+    float l = sink ? expf(-m) : 0.f;
     for (int s = 0; s < splits; ++s) l += lsum[s] * wgt[s];        // in split order
     const float inv = l > 0.f ? 1.f / l : 0.f;
     const int row = q_start[b];
@@ -430,7 +434,7 @@ int mi_attn_mix_tc_splits(int span) { return (span + kTcSplitKeys - 1) / kTcSpli
 int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, const float* mix, const int* block_table,
                    const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
                    int max_q_len, int H, int G, int dk, int dv, int page_size, int max_pages, int window,
-                   float scale, float cap, int splits, int keep_first, int vrs, cudaStream_t stream) {
+                   float scale, float cap, int splits, int keep_first, int vrs, int sink, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return kOk;
     if (keep_first < 0 || vrs < dv || vrs % 8) {
         set_last_error("mixed-head attention (tensor cores): %d kept first keys, value rows of %d every %d elements",
@@ -456,7 +460,7 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
         launch_dependent(attn_mix_tc_kernel<HPW, NT, KT>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)q, \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, mix, block_table, q_start, \
                          kv_len, (__nv_bfloat16*)out, part_o, part_ml, H, G, dk, page_size, max_pages, window,  \
-                         scale, cap, splits, hgroups, keep_first, vrs);                                         \
+                         scale, cap, splits, hgroups, keep_first, vrs, sink);                                   \
     } while (0)
 #define MI_TC_KT(HPW, NT) do { if (kt == 32) MI_TC_LAUNCH(HPW, NT, 32); else MI_TC_LAUNCH(HPW, NT, 16); } while (0)
     if (dv == 128) {
@@ -472,7 +476,7 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
         if (merge_smem > 48 * 1024)
             cudaFuncSetAttribute(attn_mix_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem);
         launch_dependent(attn_mix_merge_kernel, dim3(H, B), dim3(128), merge_smem, stream, (const float*)part_o,
-                         (const float*)part_ml, q_start, (__nv_bfloat16*)out, H, dv, splits);
+                         (const float*)part_ml, q_start, (__nv_bfloat16*)out, H, dv, splits, sink);
         launched = 2;
     }
     return finish_launch("attn_mix_tc", launched);

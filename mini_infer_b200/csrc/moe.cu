@@ -281,6 +281,10 @@ moe_router_logits_small_kernel(const AT* __restrict__ x, const WT* __restrict__ 
     router_logits_small_block<AT, WT, RT_TOK>(x, wr, wsg, z, T, H, E, blockIdx.x, blockIdx.y * RT_TOK);
 }
 
+// `norm_topk` of the selection carries two switches: bit 0, the chosen weights are divided by their sum; bit 1
+// (kScoreSigmoid), the experts are scored one by one with the logistic function instead of by a softmax.
+constexpr int kScoreSigmoid = 2;
+
 // Softmax over all experts, K rounds of arg-max (lowest index among equals), weights; one warp per
 // token.  `p` is the warp's E floats of shared memory and holds the token's logits, `mx` the largest
 // of the lane's own, `gate_logit` (lane 0) the shared expert's.
@@ -290,6 +294,40 @@ __device__ __forceinline__ void router_select_loaded(float mx, float gate_logit,
                                                      float* p, int* idx_copy, int t, int E, int K, int norm_topk) {
     const int lane = threadIdx.x & 31;
     if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-gate_logit));
+    if (norm_topk & kScoreSigmoid) {
+        // every expert scored by itself, s = 1 / (1 + exp(-z)): the K largest logits are chosen (the order of
+        // the scores, and still an order where the scores have run into 1), the weights are their scores
+        if (probs_out)
+            for (int e = lane; e < E; e += 32) probs_out[(int64_t)t * E + e] = 1.0f / (1.0f + expf(-p[e]));
+        __syncwarp();
+        float wsum = 0.f, my_w = 0.f;
+        for (int k = 0; k < K; ++k) {
+            float best = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = p[e];
+                if (v > best) { best = v; bi = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+            }
+            if (bi == 0x7fffffff) bi = 0;       // logits that are not numbers: any expert, never an index outside
+            const float sc = 1.0f / (1.0f + expf(-best));
+            if (lane == k) my_w = sc;
+            wsum += sc;
+            if (lane == 0) {
+                topk_idx[(int64_t)t * K + k] = bi;
+                if (idx_copy) idx_copy[t * K + k] = bi;
+                p[bi] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        if (lane < K) topk_w[(int64_t)t * K + lane] = (norm_topk & 1) ? my_w / wsum : my_w;
+        return;
+    }
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
@@ -329,7 +367,7 @@ __device__ __forceinline__ void router_select_loaded(float mx, float gate_logit,
         }
         __syncwarp();
     }
-    if (lane < K) topk_w[(int64_t)t * K + lane] = norm_topk ? my_w / wsum : my_w;
+    if (lane < K) topk_w[(int64_t)t * K + lane] = (norm_topk & 1) ? my_w / wsum : my_w;
 }
 
 // the logits of token t in global memory, read around L1 (other blocks of the same launch may have written them)
@@ -375,6 +413,19 @@ moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restr
     if (t >= T) return;
     router_select_token(z, has_gate, topk_idx, topk_w, gate, probs_out, smem + warp * E, nullptr, t, E, K,
                         norm_topk, bias);
+}
+
+// out[dest[i]] = w[i] * x[i / K] for every (token, slot) pair i: the rows of an expert block whose weights
+// scale the experts' INPUTS, laid out in expert order.  One block per pair.
+template <typename AT>
+__global__ void __launch_bounds__(128)
+scatter_rows_scaled_kernel(const AT* __restrict__ x, const int* __restrict__ dest, const float* __restrict__ w,
+                           AT* __restrict__ out, int K, int H) {
+    wait_for_earlier_kernels();
+    const int64_t i = blockIdx.x;
+    const int64_t t = i / K, r = dest ? dest[i] : i;
+    const float wi = w[i];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) out[r * H + c] = from_float<AT>(wi * to_float(x[t * H + c]));
 }
 
 // ---------------------------------------------------------------------------
@@ -958,6 +1009,16 @@ int mi_moe_norm_route_small(float* hidden, const float* delta, const void* norm_
 }
 
 // `counts_scratch` is not used any more (the signature is kept).
+int mi_scatter_rows_scaled(const void* x, const int* dest, const float* w, void* out, int adtype, int n_pairs, int K,
+                           int H, cudaStream_t stream) {
+    if (n_pairs <= 0 || H <= 0) return kOk;
+    if (K < 1 || !w) { set_last_error("scatter_rows_scaled: %d slots per token, weights %p", K, (const void*)w); return kBadShape; }
+    MI_DISPATCH_1(adtype, AT,
+        launch_dependent(scatter_rows_scaled_kernel<AT>, dim3(n_pairs), dim3(128), 0, stream, (const AT*)x, dest, w,
+                         (AT*)out, K, H));
+    return finish_launch("scatter_rows_scaled");
+}
+
 int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* inv_perm, int* counts_scratch, int T,
                    int E, int K, cudaStream_t stream) {
     if (E + 1 > 12000) {

@@ -9,6 +9,10 @@
 //   concat_cast           out[t] = [hidden[t] + a[t] + b[t] | other[t]] in the activation type: the input
 //                         of a projection that reads the residual beside a second stream
 //   rows_plus_vec         hidden[t] = y[t] + vec: a projection's result becomes the residual, plus one row
+//   out_norm_add          hidden[t] += mult * y[t] / rms(y[t]) * w, and the new row once more in the activation
+//                         type: a block whose parts read the residual itself and whose OUTPUT is normalised;
+//                         y may be a sum of rows that is formed here and never written out
+//   softcap_rows          z <- cap * tanh(z / cap) in place (capped logits)
 
 #include "common.cuh"
 
@@ -133,6 +137,71 @@ rows_plus_vec_kernel(float* __restrict__ hidden, const float* __restrict__ y, co
     for (int i = threadIdx.x; i < H; i += blockDim.x) hidden[t * H + i] = y[t * H + i] + to_float(vec[i]);
 }
 
+// y[t] = sum_k wk[t, k] * rows[index[t, k]] + scale[t] * extra[t], or a tensor as it is.  `wk` null: weights of
+// one; `index` null: rows t * K + k.  Added in slot order, the extra term last.
+struct RowSum {
+    const float* y;         // [T, H] or null
+    const float* rows;      // [N, H]
+    const int* index;       // [T, K] or null
+    const float* wk;        // [T, K] or null
+    const float* extra;     // [T, H] or null
+    const float* scale;     // [T] (with extra)
+    int K;
+};
+
+__device__ __forceinline__ float row_sum_at(const RowSum& s, int64_t t, int i, int H) {
+    if (s.y) return s.y[t * H + i];
+    float v = 0.f;
+    for (int k = 0; k < s.K; ++k) {
+        const int64_t r = s.index ? s.index[t * s.K + k] : t * s.K + k;
+        const float x = s.rows[r * H + i];
+        v += s.wk ? s.wk[t * s.K + k] * x : x;
+    }
+    if (s.extra) v += s.scale[t] * s.extra[t * H + i];
+    return v;
+}
+
+// One block per row.  The sum of squares runs in an order that depends on H only.
+template <typename AT, typename WT>
+__global__ void __launch_bounds__(256)
+out_norm_add_kernel(float* __restrict__ hidden, RowSum s, const WT* __restrict__ w, AT* __restrict__ x_out, int H,
+                    float eps, float mult) {
+    extern __shared__ float yrow[];             // [H] when it fits (else the sum is formed twice)
+    __shared__ float scratch[32];
+    wait_for_earlier_kernels();
+    const int64_t t = blockIdx.x;
+    const bool staged = H <= 8192;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = row_sum_at(s, t, i, H);
+        if (staged) yrow[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rr = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = staged ? yrow[i] : row_sum_at(s, t, i, H);
+        const float h = hidden[t * H + i] + mult * (v * rr * to_float(w[i]));
+        hidden[t * H + i] = h;
+        if (x_out) x_out[t * H + i] = from_float<AT>(h);
+    }
+}
+
+__global__ void softcap_rows_kernel(float* __restrict__ z, int64_t total, float cap) {
+    wait_for_earlier_kernels();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x)
+        z[idx] = cap * tanhf(z[idx] / cap);
+}
+
+template <typename AT>
+__global__ void cast_rows_kernel(const float* __restrict__ x, AT* __restrict__ out, int64_t total) {
+    wait_for_earlier_kernels();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x)
+        out[idx] = from_float<AT>(x[idx]);
+}
+
 }  // namespace mi
 
 using namespace mi;
@@ -194,6 +263,41 @@ int mi_rows_plus_vec(float* hidden, const float* y, const void* vec, int wdtype,
     MI_DISPATCH_1(wdtype, WT,
         launch_dependent(rows_plus_vec_kernel<WT>, dim3(T), dim3(256), 0, stream, hidden, y, (const WT*)vec, H));
     return finish_launch("rows_plus_vec");
+}
+
+int mi_out_norm_add(float* hidden, const float* y, const float* rows, const int* index, const float* wk,
+                    const float* extra, const float* scale, int K, const void* w, int wdtype, void* x_out, int adtype,
+                    int T, int H, float eps, float mult, cudaStream_t stream) {
+    if (T <= 0 || H <= 0) return kOk;
+    if (!y && (!rows || K < 1)) { set_last_error("out_norm_add: neither a tensor nor rows to add"); return kBadShape; }
+    if ((extra == nullptr) != (scale == nullptr)) {
+        set_last_error("out_norm_add: the extra term and its scale come together");
+        return kBadShape;
+    }
+    const RowSum s{y, rows, index, wk, extra, scale, K};
+    const size_t smem = H <= 8192 ? sizeof(float) * H : 0;
+    MI_DISPATCH_2(adtype, AT, wdtype, WT,
+        launch_dependent(out_norm_add_kernel<AT, WT>, dim3(T), dim3(256), smem, stream, hidden, s, (const WT*)w,
+                         (AT*)x_out, H, eps, mult));
+    return finish_launch("out_norm_add");
+}
+
+int mi_softcap_rows(float* z, int64_t total, float cap, cudaStream_t stream) {
+    if (total <= 0) return kOk;
+    if (!(cap > 0.f)) { set_last_error("softcap_rows: the cap must be positive"); return kBadShape; }
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    launch_dependent(softcap_rows_kernel, dim3((int)blocks), dim3(256), 0, stream, z, total, cap);
+    return finish_launch("softcap_rows");
+}
+
+int mi_cast_rows(const float* x, void* out, int adtype, int64_t total, cudaStream_t stream) {
+    if (total <= 0) return kOk;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    MI_DISPATCH_1(adtype, AT,
+        launch_dependent(cast_rows_kernel<AT>, dim3((int)blocks), dim3(256), 0, stream, x, (AT*)out, total));
+    return finish_launch("cast_rows");
 }
 
 }  // extern "C"

@@ -183,6 +183,7 @@ class Model:
 
     def _forward(self, ctx: StepContext, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         hidden = self.embedding.forward(ctx.token_ids)
+        ctx.carried.clear()
         if self._keeps_embedding_output:
             ctx.embedding_output = hidden.clone()       # the residual stream is updated in place from here on
         pending = None
@@ -201,9 +202,11 @@ class Model:
             pending = layer.block.forward(layer, hidden, pending, ctx, self.bindings[pos])
             if self.layer_observer is not None:
                 # the addition of a part's output is left to the next norm's kernel; form it here
-                self.layer_observer(pos, hidden if pending is None else hidden + resolve(pending))
+                left = resolve(pending)
+                self.layer_observer(pos, hidden if left is None else hidden + left)
         if ctx.prefetch is not None:
             ctx.prefetch.join()
+        ctx.carried.clear()
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         x = apply_norm(self.final_norm, hidden, pending, rows=logit_rows)

@@ -484,11 +484,19 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return out
 
 
+def _selection_mode(norm_topk: bool, scoring: str) -> int:
+    if scoring not in ("softmax", "sigmoid"):
+        raise ValueError(f"router scoring '{scoring}' is not 'softmax' or 'sigmoid'")
+    return int(bool(norm_topk)) | (2 if scoring == "sigmoid" else 0)
+
+
 def moe_router(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
-               norm_topk: bool, want_probs: bool = False, bias: Optional[torch.Tensor] = None
+               norm_topk: bool, want_probs: bool = False, bias: Optional[torch.Tensor] = None,
+               scoring: str = "softmax"
                ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Router of one layer.  Returns ``(idx [T,K] int32, w [T,K] f32, gate [T] f32 | None, probs | None)``.
-    ``bias`` (float32 ``[E]``) is added to the logits before the softmax and the choice."""
+    ``bias`` (float32 ``[E]``) is added to the logits before the softmax and the choice.  ``scoring``
+    ``sigmoid``: every expert's score is ``1 / (1 + exp(-logit))`` by itself instead of the softmax."""
     _chk(x, "moe_router x")
     T, H = x.shape
     _chk(router_w, "moe_router weight", None, (None, H))
@@ -506,7 +514,8 @@ def moe_router(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[
     z = torch.empty(T, E + 1, dtype=F32, device=dev)
     check(library().mi_moe_router(_ptr(x), _code(x, "moe_router x"), _ptr(router_w), _ptr(shared_gate_w),
                                   _code(router_w, "moe_router weight"), _ptr(z), _ptr(idx), _ptr(w), _ptr(gate),
-                                  _ptr(probs), T, H, E, int(top_k), int(bool(norm_topk)), _ptr(bias), _stream()),
+                                  _ptr(probs), T, H, E, int(top_k), _selection_mode(norm_topk, scoring), _ptr(bias),
+                                  _stream()),
           "moe_router")
     return idx, w, gate, probs
 
@@ -536,7 +545,7 @@ def route_small_max_tokens() -> int:
 
 def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
                     norm_topk: bool, ticket: torch.Tensor, want_probs: bool = False, permute: bool = True,
-                    bias: Optional[torch.Tensor] = None):
+                    bias: Optional[torch.Tensor] = None, scoring: str = "softmax"):
     """:func:`moe_router` and (with ``permute``) :func:`moe_permute` of a step of a few tokens in
     one launch.
 
@@ -571,8 +580,8 @@ def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Opti
     check(library().mi_moe_route_small(
         _ptr(x), _code(x, "moe_route_small x"), _ptr(router_w), _ptr(shared_gate_w),
         _code(router_w, "moe_route_small weight"), _ptr(z), _ptr(ticket), _ptr(idx), _ptr(w), _ptr(gate), _ptr(probs),
-        _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T, H, E, int(top_k), int(bool(norm_topk)), _ptr(bias),
-        _stream()), "moe_route_small")
+        _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T, H, E, int(top_k), _selection_mode(norm_topk, scoring),
+        _ptr(bias), _stream()), "moe_route_small")
     return idx, w, gate, probs, offsets, sorted_token, inv_perm
 
 
@@ -840,6 +849,25 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def scatter_rows_scaled(x: torch.Tensor, dest: Optional[torch.Tensor], weights: torch.Tensor) -> torch.Tensor:
+    """``out[dest[t * K + k]] = weights[t, k] * x[t]`` (``dest`` None: row ``t * K + k``): the inputs of an expert
+    block whose weights scale what the experts read, laid out in expert order.  The product is formed in float32
+    and rounded once to the type of ``x``."""
+    _chk(x, "scatter_rows_scaled x")
+    T, H = x.shape
+    _chk(weights, "scatter_rows_scaled weights", F32, (T, None))
+    K = weights.shape[1]
+    _chk(dest, "scatter_rows_scaled dest", I32)
+    if dest is not None and dest.numel() != T * K:
+        raise ValueError(f"scatter_rows_scaled: {dest.numel()} places for {T * K} (token, slot) pairs")
+    out = torch.empty(T * K, H, dtype=x.dtype, device=x.device)
+    if DEBUG_BOUNDS:
+        _dbg_range(dest, 0, T * K, "scatter_rows_scaled dest")
+    check(library().mi_scatter_rows_scaled(_ptr(x), _ptr(dest), _ptr(weights), _ptr(out), _code(x, "scatter_rows_scaled x"),
+                                           T * K, K, H, _stream()), "scatter_rows_scaled")
+    return out
+
+
 _tc_status = {}
 _tc_pending = False
 
@@ -967,6 +995,59 @@ def add2_rmsnorm_scalar(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Opti
                                            _ptr(out1), _ptr(out2), _code(out1, "add2_rmsnorm_scalar out"), n, H,
                                            float(eps), _stream()), "add2_rmsnorm_scalar")
     return out1, out2
+
+
+def out_norm_add(hidden: torch.Tensor, y, weight: torch.Tensor, eps: float, mult: float,
+                 out_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
+    """``hidden += mult * y / rms(y) * weight`` row by row (float32), and the new rows once more in ``out_dtype``
+    (None: not wanted).  ``y`` is a float32 tensor ``[T, H]`` or the tuple ``(rows, index, weights, extra,
+    scale)`` of a sum of rows, ``y[t] = sum_k weights[t, k] rows[index[t, k]] + scale[t] extra[t]`` (``weights``
+    None: ones, then ``index`` gives the number of slots; ``index`` None: rows in order), which is formed inside
+    the kernel and never written out."""
+    _chk(hidden, "out_norm_add hidden", F32)
+    T, H = hidden.shape
+    _chk(weight, "out_norm_add weight", None, (H,))
+    yt = rows = index = wk = extra = scale = None
+    K = 0
+    if isinstance(y, torch.Tensor):
+        yt = y
+        _chk(yt, "out_norm_add y", F32, (T, H))
+    else:
+        rows, index, wk, extra, scale = y
+        _chk(rows, "out_norm_add rows", F32, (None, H))
+        _chk(index, "out_norm_add index", I32)
+        _chk(wk, "out_norm_add weights", F32)
+        _chk(extra, "out_norm_add extra", F32, (T, H))
+        _chk(scale, "out_norm_add scale", F32, (T,))
+        n = wk.numel() if wk is not None else (index.numel() if index is not None else rows.shape[0])
+        if T == 0 or n % T:
+            raise ValueError(f"out_norm_add: {n} slots for {T} rows")
+        K = n // T
+        if index is None and rows.shape[0] != T * K:
+            raise ValueError(f"out_norm_add: {rows.shape[0]} rows in order for {T} x {K} slots")
+        if DEBUG_BOUNDS:
+            _dbg_range(index, 0, rows.shape[0], "out_norm_add index")
+    out = torch.empty(T, H, dtype=out_dtype, device=hidden.device) if out_dtype is not None else None
+    check(library().mi_out_norm_add(_ptr(hidden), _ptr(yt), _ptr(rows), _ptr(index), _ptr(wk), _ptr(extra), _ptr(scale),
+                                    K, _ptr(weight), _code(weight, "out_norm_add weight"), _ptr(out),
+                                    _CODES[out_dtype] if out_dtype is not None else 0, T, H, float(eps), float(mult),
+                                    _stream()), "out_norm_add")
+    return out
+
+
+def softcap_rows(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """``z <- cap * tanh(z / cap)`` in place (float32)."""
+    _chk(z, "softcap_rows z", F32)
+    check(library().mi_softcap_rows(_ptr(z), z.numel(), float(cap), _stream()), "softcap_rows")
+    return z
+
+
+def cast_rows(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Float32 rows rounded to ``out_dtype``."""
+    _chk(x, "cast_rows x", F32)
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(library().mi_cast_rows(_ptr(x), _ptr(out), _code(out, "cast_rows out"), x.numel(), _stream()), "cast_rows")
+    return out
 
 
 def geglu_tanh(gu: torch.Tensor) -> torch.Tensor:
@@ -1142,12 +1223,25 @@ def rope_store(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[to
                slot_mapping: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, nh: int, nkv: int,
                dk: int, dv: int, page_size: int, out_dtype: torch.dtype,
                q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
-               eps: float = 0.0) -> torch.Tensor:
+               eps: float = 0.0, neighbours: bool = False, v_first: Optional[torch.Tensor] = None,
+               blend: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rotary encoding of the first ``rot_dim`` dimensions of the query and key heads of float32 rows
     ``[nh*dk | nkv*dk | nkv*dv]``, cache write of keys ``[pages, nkv, page_size, dk]`` and values
     ``[pages, nkv, page_size, dv]`` (slot -1: not written).  With ``q_gain`` and ``k_gain`` (float32
     ``[dk]``) every query and key head is first divided by its root mean square (``eps`` inside the root) and
-    multiplied by the gain.  Returns ``q [T, nh, dk]`` in ``out_dtype``."""
+    multiplied by the gain.  The rotation pairs dimension ``i`` with ``i + rot_dim / 2``, or, with
+    ``neighbours``, dimension ``2i`` with ``2i + 1``.  With ``v_first`` (float32 ``[T, nkv*dv]``; rows may be a
+    column slice of a wider matrix) and ``blend`` (one float32 on the device) the values that are cached are
+    ``(1 - blend) v + blend v_first``.  Returns ``q [T, nh, dk]`` in ``out_dtype``."""
+    vf_stride = 0
+    if v_first is not None:
+        if (not v_first.is_cuda or v_first.dtype != F32 or v_first.dim() != 2 or v_first.stride(1) != 1
+                or tuple(v_first.shape) != (qkv.shape[0], nkv * dv)):
+            raise ValueError(f"rope_store: v_first must be float32 [{qkv.shape[0]}, {nkv * dv}] with unit column stride")
+        _chk(blend, "rope_store blend", F32, (1,))
+        if blend is None:
+            raise ValueError("rope_store: v_first comes with its blending weight")
+        vf_stride = v_first.stride(0)
     _chk(q_gain, "rope_store q_gain", F32, (dk,))
     _chk(k_gain, "rope_store k_gain", F32, (dk,))
     _chk(qkv, "rope_store qkv", F32)
@@ -1165,7 +1259,9 @@ def rope_store(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[to
         _dbg_range(slot_mapping, -1, k_cache.shape[0] * page_size, "rope_store slot_mapping")
     check(library().mi_rope_store(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slot_mapping), _ptr(q),
                                   _ptr(k_cache), _ptr(v_cache), _code(q, "rope_store q"), T, nh, nkv, dk, dv,
-                                  int(rot_dim), page_size, _ptr(q_gain), _ptr(k_gain), float(eps), _stream()),
+                                  int(rot_dim), page_size, _ptr(q_gain), _ptr(k_gain), float(eps),
+                                  int(bool(neighbours)), _ptr(v_first), int(vf_stride),
+                                  _ptr(blend) if v_first is not None else None, _stream()),
           "rope_store")
     return q
 
@@ -1177,12 +1273,13 @@ def attention_mix_supported(nh: int, nkv: int, dk: int, dv: int, dtype: torch.dt
 def attention_mix(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, mix: Optional[torch.Tensor],
                   block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int,
                   window: int, scale: float, softcap: float, keep_first: int = 0,
-                  value_dim: int = 0) -> torch.Tensor:
+                  value_dim: int = 0, sink: bool = False) -> torch.Tensor:
     """Attention of a ragged batch over the paged cache with ``score <- softcap * tanh(score / softcap)``
     (``softcap`` 0: none) and then ``score_h <- sum_g mix[h, g] score_g`` (``mix`` None: none) before the
     softmax over the visible keys: key ``j`` is visible from position ``p`` iff ``j <= p`` and (``window`` is
     0 or ``j > p - window`` or ``j < keep_first``).  With ``value_dim`` a token's value is the first
-    ``value_dim`` numbers of its row of ``v_cache`` (which may be the key cache itself).
+    ``value_dim`` numbers of its row of ``v_cache`` (which may be the key cache itself).  With ``sink`` the
+    softmax counts one key more, of score 0 and without a value: ``p_j = exp(s_j) / (1 + sum exp(s_j))``.
     Returns ``[T, nh, dv]``."""
     _chk(q, "attention_mix q")
     T, nh, dk = q.shape
@@ -1207,7 +1304,7 @@ def attention_mix(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     check(library().mi_attn_mix(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "attention_mix q"), _ptr(mix),
                                 _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), B, int(max_q_len), nh, nkv,
                                 dk, dv, page_size, max_pages, int(window), float(scale), float(softcap),
-                                int(keep_first), vrs, _stream()), "attention_mix")
+                                int(keep_first), vrs, int(bool(sink)), _stream()), "attention_mix")
     return out
 
 
@@ -1226,7 +1323,7 @@ def attention_mix_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int,
                      window: int, scale: float, softcap: float, splits: int = 1,
                      part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                     keep_first: int = 0, value_dim: int = 0) -> torch.Tensor:
+                     keep_first: int = 0, value_dim: int = 0, sink: bool = False) -> torch.Tensor:
     """:func:`attention_mix` on the tensor cores (bfloat16).  ``splits > 1`` (steps of one token per request
     only): the keys of a request are cut into ``splits`` blocks whose partial results go through the float32
     scratch ``part_o`` (``B * splits * nh * dv``) and ``part_ml`` (``B * splits * nh * 2``); with
@@ -1256,7 +1353,7 @@ def attention_mix_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     check(library().mi_attn_mix_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(mix), _ptr(block_table), _ptr(q_start),
                                    _ptr(kv_len), _ptr(out), _ptr(part_o), _ptr(part_ml), B, int(max_q_len), nh, nkv, dk,
                                    dv, page_size, max_pages, int(window), float(scale), float(softcap), int(splits),
-                                   int(keep_first), vrs, _stream()), "attention_mix_tc")
+                                   int(keep_first), vrs, int(bool(sink)), _stream()), "attention_mix_tc")
     return out
 
 

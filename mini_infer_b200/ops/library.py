@@ -51,9 +51,13 @@ _SIGNATURES = {
     "mi_delta_scan": [P, I, P, I, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, P],
     "mi_ssd_scan": [P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, P],
     "mi_gated_group_rmsnorm": [P, P, I, P, I, I, P, I, I, I, I, I, F, P],
-    "mi_rope_store": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, F, P],
-    "mi_attn_mix": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, P],
-    "mi_attn_mix_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, P],
+    "mi_rope_store": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, F, I, P, L, P, P],
+    "mi_attn_mix": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, P],
+    "mi_attn_mix_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, I, P],
+    "mi_out_norm_add": [P, P, P, P, P, P, P, I, P, I, P, I, I, I, F, F, P],
+    "mi_softcap_rows": [P, L, F, P],
+    "mi_cast_rows": [P, P, I, L, P],
+    "mi_scatter_rows_scaled": [P, P, P, P, I, I, I, I, P],
     "mi_add2_rmsnorm_scalar": [P, P, P, P, P, P, P, P, I, I, I, F, P],
     "mi_geglu_tanh": [P, P, I, L, I, P],
     "mi_concat_cast": [P, P, P, P, P, I, I, I, P],

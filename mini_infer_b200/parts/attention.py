@@ -78,6 +78,9 @@ class GQAttention(Mixer):
             self.b_qkv = torch.cat(bs, dim=0).contiguous()
         self.w_o = prec.matrix(tensors[f"{self.prefix}o_proj.weight"], dev)
         self.inv_freq = self.position.table(dev)
+        if getattr(self.position, "pairing", "halves") != "halves":
+            raise ValueError("attention: this part's kernels rotate by halves; a rotation of neighbouring "
+                             "dimensions belongs to 'head_mix_attention'")
         self.rot_dim = self.position.rot_dim if self.inv_freq is not None else self.d
         self._tensor_core_prefill = rt.act == torch.bfloat16 and F.prefill_attention_supported(self.d)
         # decode-sized steps: projection, bias, rotation and cache write in one kernel

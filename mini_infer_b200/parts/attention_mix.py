@@ -9,6 +9,12 @@ heads may differ in size.  One library product for q, k and v together, one kern
 cache write, one attention kernel that owns all heads of its queries (the mix couples them), one library product
 for the output.  Without a mix and a cap the heads are independent: prompt portions in bfloat16 then take the
 engine's tcgen05 attention where keys and values have one size that kernel is built for.
+
+Two further options.  ``sink``: the softmax counts one key more, whose score is 0 and which has no value,
+``p_j = exp(s_j) / (1 + sum exp(s_j))``, so a query may give its weight to nothing.  ``value_blend``: the layers
+that name the same blend share the FIRST such layer's values of a token: every later one caches and attends over
+``(1 - lam) v + lam v_first`` with its own ``lam`` (one number in the checkpoint); the first one's values travel
+through the step (``StepContext.carried``), since all layers of a step see the same tokens.
 """
 
 from __future__ import annotations
@@ -29,13 +35,17 @@ class HeadMixAttention(Mixer):
     request stay visible, at their true positions; 0 = none), ``scale``, ``softcap`` (0 = none), ``head_mix``
     (the layer has a ``[heads, heads]`` matrix that mixes the heads' scores), ``qk_norm`` (``{"eps": ...}``:
     every query and key head is divided by its root mean square and multiplied by a gain per dimension that
-    the heads share, before the rotation), ``position`` (a ``PartSpec`` of category ``position``), optional
+    the heads share, before the rotation), ``position`` (a ``PartSpec`` of category ``position``; its
+    ``pairing`` says which dimensions turn together), ``sink`` (the softmax's denominator counts one more key of
+    score 0), ``value_blend`` (``{"name": ..., "first": bool, "tensor": "vmix", "declared": bool}``: the
+    layers of one ``name`` blend their values with those of the layer marked ``first``; ``declared`` says
+    whether the checkpoint holds this layer's weight, which the first layer never reads), optional
     tensor names ``q``, ``k``, ``v``, ``o``, ``mix``, ``q_norm``, ``k_norm`` below the prefix.
 
     Tensors: ``<prefix>q [heads*head_dim, hidden]``, ``<prefix>k [kv_heads*head_dim, hidden]``,
     ``<prefix>v [kv_heads*value_dim, hidden]``, ``<prefix>o [hidden, heads*value_dim]``,
     ``<prefix>talk [heads, heads]`` if ``head_mix``, ``<prefix>q.norm``, ``<prefix>k.norm [head_dim]`` if
-    ``qk_norm``."""
+    ``qk_norm``, ``<prefix>vmix []`` if ``value_blend``."""
 
     graph_safe = True
     kernel_files = ("attention_mix.cu", "attention_mix_tc.cu", "attention_prefill_tc.cu")
@@ -54,6 +64,13 @@ class HeadMixAttention(Mixer):
         self.scale = float(p.get("scale", self.dk ** -0.5))
         self.softcap = float(p.get("softcap", 0.0) or 0.0)
         self.head_mix = bool(p.get("head_mix", False))
+        self.sink = bool(p.get("sink", False))
+        self.blend = dict(p["value_blend"]) if p.get("value_blend") else None
+        if self.blend is not None:
+            self.blend_key = "value_blend:" + str(self.blend["name"])
+            self.blend_first = bool(self.blend.get("first", False))
+            self.blend_tensor = prefix + self.blend.get("tensor", "vmix")
+            self.blend_declared = bool(self.blend.get("declared", True))
         pos: PartSpec = p.get("position") or PartSpec("none")
         self.position = part_class("position", pos.kind)(pos.params, prefix)
         if self.nkv < 1 or self.nh % self.nkv:
@@ -69,6 +86,8 @@ class HeadMixAttention(Mixer):
             out.append(TensorDecl(n["mix"], (self.nh, self.nh), "head_mix"))
         if self.qk_norm is not None:
             out += [TensorDecl(n["q_norm"], (self.dk,), "norm"), TensorDecl(n["k_norm"], (self.dk,), "norm")]
+        if self.blend is not None and self.blend_declared:
+            out.append(TensorDecl(self.blend_tensor, (), "blend"))
         out.append(TensorDecl(n["o"], (self.H, self.nh * self.dv)))
         return out
 
@@ -88,13 +107,22 @@ class HeadMixAttention(Mixer):
             self.qk_eps = float(self.qk_norm["eps"])
         self.inv_freq = self.position.table(dev)
         self.rot_dim = self.position.rot_dim if self.inv_freq is not None else 0
+        self.neighbours = getattr(self.position, "pairing", "halves") == "neighbours"
+        # the blending weight joins float arithmetic (the first layer of a blend has none to apply)
+        self.blend_weight = None
+        if self.blend is not None and not self.blend_first:
+            if not self.blend_declared:
+                raise ValueError(f"attention: '{self.blend_tensor}' is missing, and only the first layer of a "
+                                 f"value blend does without its weight")
+            self.blend_weight = tensors[self.blend_tensor].to(device=dev, dtype=torch.float32).reshape(1).contiguous()
         if not F.attention_mix_supported(self.nh, self.nkv, self.dk, self.dv, rt.act):
             raise ValueError(f"attention: {self.nh} heads of key size {self.dk} and value size {self.dv} "
                              f"are more than one block of the kernel holds")
 
         # bfloat16: scores and P.V on the tensor cores where the kernel is built for the sizes
         self._tensor_cores = rt.act == torch.bfloat16 and F.attention_mix_tc_supported(self.nh, self.nkv, self.dk, self.dv)
-        self._independent_heads = self.mix is None and self.softcap == 0.0 and self.dk == self.dv
+        self._independent_heads = (self.mix is None and self.softcap == 0.0 and self.dk == self.dv
+                                   and not self.sink)
         # prompt portions on the tensor-memory attention: its blocks want whole SMs (a block arrangement that
         # runs another part beside this one asks)
         self.large_steps_fill_the_device = self._tensor_cores and self._independent_heads
@@ -118,19 +146,30 @@ class HeadMixAttention(Mixer):
         view = ctx.kv_groups[cache.group]
         kc, vc = view.k[cache.layer_slot], view.v[cache.layer_slot]
         qkv = linear(x, self.w_qkv, torch.float32)
+        v_first = None
+        if self.blend is not None:
+            if self.blend_first:
+                # this layer's values, as projected, for the later layers of the blend (a view: the rows stay
+                # alive with the step)
+                ctx.carried[self.blend_key] = qkv[:, (self.nh + self.nkv) * self.dk:]
+            else:
+                v_first = ctx.carried.get(self.blend_key)
+                if v_first is None or v_first.shape[1] != self.nkv * self.dv:
+                    raise ValueError(f"attention: the first layer of the value blend '{self.blend['name']}' has "
+                                     f"not run in this step, or its values have another size")
         q = F.rope_store(qkv, ctx.positions, self.inv_freq, self.rot_dim, view.slot_mapping, kc, vc, self.nh,
                          self.nkv, self.dk, self.dv, view.page_size, self.rt.act, self.q_gain, self.k_gain,
-                         self.qk_eps)
+                         self.qk_eps, neighbours=self.neighbours, v_first=v_first, blend=self.blend_weight)
         if not self._tensor_cores:
             # float32: one kernel for every step, sums in an order that the cut of the step cannot change
             a = F.attention_mix(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
-                                self.window, self.scale, self.softcap, self.keep_first)
+                                self.window, self.scale, self.softcap, self.keep_first, sink=self.sink)
         elif ctx.all_decode and "attn_mix_part_o" in ctx.scratch:
             # one token per request: a block per request could not pull a window of keys fast enough
             splits = F.attention_mix_tc_splits(self._span(ctx.max_kv_len), self.keep_first)
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, 1, self.window,
                                    self.scale, self.softcap, splits, ctx.scratch["attn_mix_part_o"],
-                                   ctx.scratch["attn_mix_part_ml"], keep_first=self.keep_first)
+                                   ctx.scratch["attn_mix_part_ml"], keep_first=self.keep_first, sink=self.sink)
         elif self._independent_heads and F.prefill_attention_tc_supported(self.dk, view.page_size):
             # heads that exchange nothing, keys and values of one size the tcgen05 kernel is built for: prompt
             # portions (and what decodes beside them) take the engine's tensor-memory attention
@@ -138,7 +177,8 @@ class HeadMixAttention(Mixer):
                                        self.window, self.scale, keep_first=self.keep_first)
         else:
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
-                                   self.window, self.scale, self.softcap, keep_first=self.keep_first)
+                                   self.window, self.scale, self.softcap, keep_first=self.keep_first,
+                                   sink=self.sink)
         return linear(a.view(ctx.num_tokens, self.nh * self.dv), self.w_o, torch.float32)
 
 

@@ -194,6 +194,9 @@ class StepContext:
     entry_args: Mapping[str, Any] = field(default_factory=dict)
     # the embedding's output [T, H] float32, kept aside for blocks that declare ``needs_embedding_output``
     embedding_output: Optional[torch.Tensor] = None
+    # what a part of one layer leaves for parts of later layers of the same step (the first blending
+    # attention layer's values, say), by name; the model empties it before every forward pass
+    carried: Dict[str, Any] = field(default_factory=dict)
     # host copies, for parts written in plain PyTorch (tests' toy parts)
     host_q_start: Sequence[int] = ()
     host_kv_len: Sequence[int] = ()
@@ -280,6 +283,17 @@ class TensorSum(Deferred):
 
     def materialize(self) -> torch.Tensor:
         return self.a + self.b
+
+
+@dataclass
+class RoundedResidual(Deferred):
+    """Nothing is left to add: the residual stream is up to date, and ``x`` is its rounding to the activation
+    type, which a block whose parts read the residual itself takes instead of rounding the rows again."""
+
+    x: torch.Tensor
+
+    def materialize(self):
+        return None
 
 
 def split_sum(pending):

@@ -18,8 +18,8 @@ import torch
 from ..config.registry import part_class, register_part
 from ..ops import functional as F
 from .tuning import TUNING
-from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, StepContext, TensorDecl, TensorSum,
-                   WeightedRowSum, apply_norm, linear, resolve, split_sum)
+from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, RoundedResidual, Runtime, StepContext,
+                   TensorDecl, TensorSum, WeightedRowSum, apply_norm, linear, resolve, split_sum)
 
 
 class PreNormResidual(Block):
@@ -78,7 +78,8 @@ class TokenEmbedding(Embedding):
 
 class LinearHead(LMHead):
     """params: ``vocab_size``, ``hidden_size``, ``tied_to`` (name of the embedding tensor, or
-    None), optional ``tensor`` (the tensor's name below the prefix, default ``weight``).  Tensor:
+    None), optional ``tensor`` (the tensor's name below the prefix, default ``weight``) and ``softcap``
+    (the logits become ``softcap * tanh(logits / softcap)``; 0 or absent: as they are).  Tensor:
     ``<prefix>weight [V, H]`` unless tied (src/model/transformer_model.cpp:355-361;
     the reference deep-copies the tied matrix, here it is the same storage)."""
 
@@ -102,7 +103,68 @@ class LinearHead(LMHead):
         self.weight = embedding_weight
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return linear(x, self.weight, torch.float32)
+        logits = linear(x, self.weight, torch.float32)
+        cap = float(self.params.get("softcap", 0.0) or 0.0)
+        return F.softcap_rows(logits, cap) if cap > 0.0 else logits
+
+
+class OutputNormResidual(Block):
+    """``x <- x + m Norm1(Mixer(x))``, then ``x <- x + m Norm2(FFN(x))``: the parts read the residual stream
+    itself, and what is normalised is their OUTPUT, scaled by one number ``m`` before it is added.
+    params: ``residual_mult`` (``m``, default 1), ``feed_forward`` (default True; False: a layer of a mixer
+    alone, with the roles ``mixer`` and ``mixer_norm`` only).  Both norms must be plain RMS norms
+    (``rms_parameters()``).
+
+    One kernel per part takes the root mean square of the part's output, adds the scaled, normalised row to
+    the float32 residual and writes the new row once more in the activation type, which is what the next part
+    reads (in the float32 path the parts read the residual's own rows).  A feed-forward that leaves the sum of
+    its experts' rows to its consumer has it formed inside that kernel.  The residual is up to date when the
+    block returns; the rounded rows travel on as a :class:`RoundedResidual`, so that a next block of this kind
+    does not round them again."""
+
+    graph_safe = True
+    accepts_deferred = True
+    kernel_files = ("residual_forms.cu",)
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.mult = float(self.params.get("residual_mult", 1.0))
+        self.has_ff = bool(self.params.get("feed_forward", True))
+        self.roles = {"mixer": "mixer", "mixer_norm": "norm"}
+        if self.has_ff:
+            self.roles.update({"feed_forward": "feed_forward", "feed_forward_norm": "norm"})
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+
+    def _input(self, hidden: torch.Tensor, pending) -> torch.Tensor:
+        if isinstance(pending, RoundedResidual):
+            return pending.x
+        left = resolve(pending)
+        if left is not None:
+            hidden.add_(left)
+        return hidden if self.rt.act == torch.float32 else F.cast_rows(hidden, self.rt.act)
+
+    def _add(self, hidden: torch.Tensor, y, norm) -> torch.Tensor:
+        rms = norm.rms_parameters()
+        if rms is None:
+            raise ValueError("output_norm_residual: the norm of a part's output must be a plain RMS norm")
+        if isinstance(y, WeightedRowSum):
+            y = (y.rows, y.index, y.weights, y.extra, y.scale)
+        else:
+            y = resolve(y)
+        x = F.out_norm_add(hidden, y, rms[0], rms[1], self.mult, None if self.rt.act == torch.float32 else self.rt.act)
+        return hidden if x is None else x
+
+    def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, caches):
+        x = self._input(hidden, pending)
+        x = self._add(hidden, layer.mixer.forward(x, ctx, caches.get("mixer")), layer.mixer_norm)
+        if self.has_ff:
+            x = self._add(hidden, layer.feed_forward.forward_deferred(x, ctx), layer.feed_forward_norm)
+        return None if x is hidden else RoundedResidual(x)
+
+    def prefetch_layer(self, layer: BuiltLayer, ctx: StepContext, caches) -> None:
+        layer.mixer.prefetch_first(ctx, caches.get("mixer"))
 
 
 class ParallelResidual(Block):
@@ -216,6 +278,7 @@ class StreamMerge(Block):
 
 register_part("block", "prenorm_residual", PreNormResidual)
 register_part("block", "parallel_residual", ParallelResidual)
+register_part("block", "output_norm_residual", OutputNormResidual)
 register_part("block", "stream_merge", StreamMerge)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("lm_head", "linear", LinearHead)

@@ -112,9 +112,14 @@ class SparseMoE(FeedForward):
     renormalised to sum to one, which makes them the softmax over the chosen logits alone);
     ``activation`` of the experts (``silu``, default, or ``clamped_swish`` with ``limit`` and optionally
     ``slope``, as in :class:`GatedMLP`); ``router_bias`` (the router has a bias per expert that joins the
-    logits before the choice); optional tensor names below the prefix: ``router`` (default
-    ``gate.weight``), ``router_bias_name`` (default ``gate.bias``), ``expert`` (a format with ``{e}``,
-    default ``experts.{e}.``), ``gate``, ``up``, ``down`` (default ``gate_proj.weight`` and so on).
+    logits before the choice); ``scoring`` (``softmax``, default, or ``sigmoid``: every expert's score is the
+    logistic function of its own logit, the largest are chosen and are the weights);
+    ``weight_input`` (the weight multiplies what the expert READS, ``sum_k expert_k(w_k x)``, instead of what
+    it puts out: the gated unit is not linear, so the two differ); optional tensor names below the prefix:
+    ``router`` (default ``gate.weight``), ``router_bias_name`` (default ``gate.bias``), ``expert`` (a format
+    with ``{e}``, default ``experts.{e}.``), ``gate``, ``up``, ``down`` (default ``gate_proj.weight`` and so
+    on; the shared expert's three matrices take the same names), ``shared`` (the shared expert's prefix,
+    default ``shared_expert.``), ``shared_gate`` (default ``shared_expert_gate.weight``).
 
     Tensors: ``<prefix>gate.weight [E, H]`` (and ``gate.bias [E]``);
     ``<prefix>experts.{e}.{gate,up}_proj.weight [mI, H]``, ``.down_proj.weight [H, mI]``;
@@ -145,6 +150,13 @@ class SparseMoE(FeedForward):
         if self.activation == "clamped_swish" and not self.limit > 0:
             raise ValueError("moe: 'clamped_swish' needs a positive 'limit'")
         self.has_router_bias = bool(p.get("router_bias", False))
+        self.scoring = p.get("scoring", "softmax")
+        if self.scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"moe: scoring '{self.scoring}' is not 'softmax' or 'sigmoid'")
+        self.weight_input = bool(p.get("weight_input", False))
+        self._shared_prefix = self.prefix + p.get("shared", "shared_expert.")
+        self._shared_gate_name = self.prefix + p.get("shared_gate", "shared_expert_gate.weight")
+        self._ones = None
         self._router_name = self.prefix + p.get("router", "gate.weight")
         self._router_bias_name = self.prefix + p.get("router_bias_name", "gate.bias")
         self._expert_format = p.get("expert", "experts.{e}.")
@@ -177,11 +189,11 @@ class SparseMoE(FeedForward):
                     TensorDecl(q + un, (self.mI, self.H)),
                     TensorDecl(q + dn, (self.H, self.mI))]
         if self.sI > 0:
-            q = p + "shared_expert."
-            out += [TensorDecl(q + "gate_proj.weight", (self.sI, self.H)),
-                    TensorDecl(q + "up_proj.weight", (self.sI, self.H)),
-                    TensorDecl(q + "down_proj.weight", (self.H, self.sI)),
-                    TensorDecl(p + "shared_expert_gate.weight", (1, self.H))]
+            q = self._shared_prefix
+            out += [TensorDecl(q + gn, (self.sI, self.H)),
+                    TensorDecl(q + un, (self.sI, self.H)),
+                    TensorDecl(q + dn, (self.H, self.sI)),
+                    TensorDecl(self._shared_gate_name, (1, self.H))]
         return out
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
@@ -202,11 +214,10 @@ class SparseMoE(FeedForward):
             self.w_down[e].copy_(tensors[q + dn])
         self.w_shared_gate = None
         if self.sI > 0:
-            q = p + "shared_expert."
-            self.w_shared_gate_up = torch.cat([m(tensors[q + "gate_proj.weight"], dev),
-                                               m(tensors[q + "up_proj.weight"], dev)], dim=0)
-            self.w_shared_down = m(tensors[q + "down_proj.weight"], dev)
-            g = rt.precision.small(tensors[p + "shared_expert_gate.weight"], dev).reshape(-1)
+            q = self._shared_prefix
+            self.w_shared_gate_up = torch.cat([m(tensors[q + gn], dev), m(tensors[q + un], dev)], dim=0)
+            self.w_shared_down = m(tensors[q + dn], dev)
+            g = rt.precision.small(tensors[self._shared_gate_name], dev).reshape(-1)
             self.w_shared_gate = g.to(self.w_router.dtype).contiguous()
         # the one-launch routing of decode-sized steps counts its blocks in these words
         self._route_small_max = F.route_small_max_tokens()
@@ -260,7 +271,7 @@ class SparseMoE(FeedForward):
         if ctx.prefetch is not None and self.sI > 0:
             # the routing that comes first hardly touches memory: the shared expert's weights arrive beside it
             ctx.prefetch((self.w_shared_gate_up, self.w_shared_down))
-        if (rms is not None and self.b_router is None
+        if (rms is not None and self.b_router is None and self.scoring == "softmax" and not self.weight_input
                 and T <= TUNING.shared_expert_fork_after_routing_max_tokens and self._by_pair(T)
                 and F.norm_route_small_takes(self.H, self.E, self.w_shared_gate is not None, self.w_router.dtype)
                 and (delta is None or isinstance(delta, torch.Tensor))):
@@ -269,6 +280,12 @@ class SparseMoE(FeedForward):
                 self.norm_topk, want_probs=self.keep_routing)
             return self._run(x, ctx, (idx, w, gate, probs))
         return super().forward_from_residual(hidden, delta, norm, ctx)
+
+    def _unit_weights(self, T: int, device) -> torch.Tensor:
+        """``[T, K]`` ones: the weights of a sum whose rows were weighted on their way in."""
+        if self._ones is None or self._ones.shape[0] < T or self._ones.device != device:
+            self._ones = torch.ones(max(T, 256), self.K, dtype=torch.float32, device=device)
+        return self._ones[:T]
 
     def _glu(self):
         """The form of the experts' gated units, as the grouped products' epilogues take it."""
@@ -297,7 +314,7 @@ class SparseMoE(FeedForward):
         shared = side = inv_perm = None
         overlap = self.sI > 0 and TUNING.shared_expert_overlap
         n = T * self.K
-        if self._by_pair(T):
+        if self._by_pair(T) and not self.weight_input:
             # decode-sized step: routing in one launch, no permutation; every used expert's weights
             # are read once and result rows are indexed by (token, slot) pair
             fork_first = T > TUNING.shared_expert_fork_after_routing_max_tokens
@@ -308,7 +325,7 @@ class SparseMoE(FeedForward):
             else:
                 idx, w, gate, probs, _, _, _ = F.moe_route_small(
                     x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
-                    want_probs=self.keep_routing, permute=False, bias=self.b_router)
+                    want_probs=self.keep_routing, permute=False, bias=self.b_router, scoring=self.scoring)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
             act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True, glu=self._glu())
@@ -325,28 +342,36 @@ class SparseMoE(FeedForward):
                     and self.rt.act == torch.bfloat16:
                 idx, w, gate, probs, offsets, sorted_token, inv_perm = F.moe_route_small(
                     x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
-                    want_probs=self.keep_routing, bias=self.b_router)
+                    want_probs=self.keep_routing, bias=self.b_router, scoring=self.scoring)
             else:
                 idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
-                                                   want_probs=self.keep_routing, bias=self.b_router)
+                                                   want_probs=self.keep_routing, bias=self.b_router,
+                                                   scoring=self.scoring)
                 offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
+            src, gather = x, sorted_token
+            if self.weight_input:
+                # the experts read w * x: one weighted copy of the token's row per chosen expert, written straight
+                # into expert order (so nothing is left to gather), and the experts' rows are summed as they are
+                src, gather = F.scatter_rows_scaled(x, inv_perm, w), None
             if self._few_rows_per_expert(T):
                 # a few rows per expert: bound by reading each used expert once
-                act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True, glu=self._glu())
+                act = F.grouped_gemm_skinny(src, gather, self.w_gate_up, offsets, n, True, glu=self._glu())
                 y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)
             elif self._tc:
                 # many rows per expert: tensor-core tiles over the rows gathered into expert order
-                xs = F.gather_rows(x, sorted_token)
+                xs = src if gather is None else F.gather_rows(x, sorted_token)
                 act = F.grouped_gemm_tc(xs, self.w_gate_up, offsets, True, glu=self._glu())
                 y = F.grouped_gemm_tc(act, self.w_down, offsets, False)
             else:
-                act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act,
+                act = F.grouped_gemm_plain(src, gather, self.w_gate_up, offsets, n, True, self.rt.act,
                                            glu=self._glu())
                 y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
         if self.keep_routing:
             self.last_routing = (idx, w, probs)
+        if self.weight_input:
+            w = self._unit_weights(T, x.device)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         elif self.sI > 0:

@@ -1,6 +1,6 @@
 """Position encodings that act on queries and keys inside the attention part.
 
-``rope``: half-split rotary encoding; ``inv_freq[i] = theta^(-2i/rot_dim)``
+``rope``: rotary encoding (half-split, or neighbouring dimensions paired); ``inv_freq[i] = theta^(-2i/rot_dim)``
 (src/layers/rope.cpp:20-29); the rotation itself, with angles computed in
 float32 from the absolute position, runs in the kernel that also adds the
 projection bias and writes the cache (reference: cos/sin tables rounded to
@@ -24,12 +24,18 @@ from .base import PositionEncoding
 
 
 class RotaryEncoding(PositionEncoding):
-    """params: ``head_dim``, ``theta``, optional ``rot_dim`` (default ``head_dim``)."""
+    """params: ``head_dim``, ``theta``, optional ``rot_dim`` (default ``head_dim``) and ``pairing``: which
+    dimensions turn together, ``halves`` (default: ``i`` with ``i + rot_dim / 2``) or ``neighbours`` (``2i``
+    with ``2i + 1``); pair ``i`` turns by ``position * theta^(-2i/rot_dim)`` either way."""
 
     graph_safe = True
+    PAIRINGS = ("halves", "neighbours")
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
+        self.pairing = self.params.get("pairing", "halves")
+        if self.pairing not in self.PAIRINGS:
+            raise ValueError(f"rope: pairing '{self.pairing}' is not one of {self.PAIRINGS}")
         d = int(self.params["head_dim"])
         self.rot_dim = int(self.params.get("rot_dim", d))
         if self.rot_dim % 2 or not 0 < self.rot_dim <= d:
@@ -72,6 +78,7 @@ class ScaledRotaryEncoding(RotaryEncoding):
 class NoPositionEncoding(PositionEncoding):
     graph_safe = True
     rot_dim = 0
+    pairing = "halves"
 
     def table(self, device) -> Optional[torch.Tensor]:
         return None

@@ -80,7 +80,8 @@ def random_tensor(shape: Tuple[int, ...], key: Tuple[int, int], std: float, offs
 
 # role of a tensor -> (mean, factor on the standard deviation): short filters and small matrices that act
 # on few inputs are drawn wider, so that what they feed is not vanishingly small
-ROLE_INIT = {"norm": (1.0, 1.0), "conv": (0.0, 15.0), "low_rank": (0.0, 8.0), "head_mix": (0.0, 15.0)}
+ROLE_INIT = {"norm": (1.0, 1.0), "conv": (0.0, 15.0), "low_rank": (0.0, 8.0), "head_mix": (0.0, 15.0),
+             "blend": (0.5, 5.0)}
 
 
 class RandomSource:
