@@ -87,10 +87,11 @@ def sink_softmax(s: torch.Tensor, visible: torch.Tensor) -> torch.Tensor:
 
 
 def blend_values(v: torch.Tensor, v_first: Optional[torch.Tensor], lam) -> torch.Tensor:
-    """``(1 - lam) v + lam v_first``; the first blending layer keeps its own values."""
+    """``(1 - lam) v + lam v_first`` over a token's values as one row (heads side by side); the first
+    blending layer keeps its own values."""
     if v_first is None:
         return v
-    return (1.0 - lam) * v + lam * v_first
+    return (1.0 - lam) * v + lam * v_first.reshape(v.shape)
 
 
 def attention_mixer(h, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, v_first, rnd: Callable = same):
@@ -154,7 +155,7 @@ def moe(h, w: Dict[str, torch.Tensor], p: str, mlp: dict, rnd: Callable = same, 
         q = p + "shared."
         g = torch.sigmoid(h @ w[q + "sg"].T)
         out = out + g * gated_unit(h, w[q + "gate"], w[q + "up"], w[q + "down"], rnd)
-    return out, idx
+    return out, (idx, scores)
 
 
 def feed_forward(h, w, p: str, mlp: dict, rnd: Callable = same, forced=None):
@@ -169,11 +170,11 @@ def feed_forward(h, w, p: str, mlp: dict, rnd: Callable = same, forced=None):
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
             rnd: Callable = same, forced: Optional[Dict[int, torch.Tensor]] = None, layers_out: Optional[list] = None,
-            routing_out: Optional[dict] = None) -> torch.Tensor:
+            chosen: Optional[dict] = None) -> torch.Tensor:
     """Logits ``[T, vocab]`` of one sequence.  ``layers_out`` collects the residual after every layer;
-    ``routing_out[layer]`` the chosen experts."""
+    ``chosen[layer] = (experts [T, top], scores [T, experts])`` what every routed layer chose."""
     w = {k: v.to(dtype) for k, v in weights.items()}
-    eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
+    eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     x = norm_plain(w["embed"][torch.tensor(tokens)], w["embed.norm"], eps)
     v_first = None
     for i, L in enumerate(cfg["layers"]):
@@ -183,11 +184,19 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
             v_first = v
         x = x + mult * norm_plain(y, w[p + "norm1"], eps)
         if L.get("mlp") is not None:
-            y, idx = feed_forward(rnd(x), w, p + "mlp.", L["mlp"], rnd, None if forced is None else forced.get(i))
-            if routing_out is not None and idx is not None:
-                routing_out[i] = idx
+            y, rec = feed_forward(rnd(x), w, p + "mlp.", L["mlp"], rnd, None if forced is None else forced.get(i))
+            if chosen is not None and rec is not None:
+                chosen[i] = rec
             x = x + mult * norm_plain(y, w[p + "norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     z = rnd(norm_plain(x, w["final.norm"], eps)) @ w["embed"].T
-    return cap(z, cfg["logit_softcap"])
+    return cap(z, cfg["logit_softcap"]) if cfg.get("logit_softcap") else z
+
+
+def greedy(cfg: dict, weights, prompt: List[int], n: int, dtype=torch.float64) -> List[int]:
+    """``n`` tokens, each the arg-max of the logits at the last position of all tokens so far."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(torch.argmax(forward(cfg, weights, toks, dtype)[-1])))
+    return toks[len(prompt):]
