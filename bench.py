@@ -777,6 +777,92 @@ def run_nipapel(args):
                        _nipapel_kernel_work, _moe_twin_kernel_work, "moe_twin", graph_prompts=True)
 
 
+# --------------------------------------------------------------------------- #
+# --tofinex: the Tofinex design beside the closest built-in model (Qwen2-MoE) at equal sizes
+# --------------------------------------------------------------------------- #
+TOFINEX_SIZES = {   # width, heads, key/value heads, head size, dense feed-forward, experts, experts per token, expert
+                    # width, shared expert width
+    "0.5b": (1024, 8, 2, 128, 2816, 16, 2, 1024, 2816),
+    "a2.7b": (2048, 16, 4, 128, 5632, 60, 4, 1408, 5632),      # the layer sizes of Qwen1.5-MoE-A2.7B
+}
+TOFINEX_LAYERS = 6
+
+
+def tofinex_config(size, window, vocab):
+    W, H, G, d, ff, E, K, eff, sff = TOFINEX_SIZES[size]
+    attn = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "rot": {"base": 500000.0, "dims": d}, "scale": d ** -0.5,
+            "softcap": 30.0, "v_mix": True}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": K}, "shared": {"ff": sff}}
+    layers = [{"type": "attention", "mixer": attn, "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe}
+              for i in range(TOFINEX_LAYERS)]
+    return {"architecture": "Tofinex", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def tofinex_twin_config(size, window, vocab):
+    """The closest built-in model: Qwen2-MoE with the same width, heads, experts, expert and shared expert
+    widths, a dense first layer of the same feed-forward width, attention over all earlier tokens, as many
+    layers."""
+    W, H, G, d, ff, E, K, eff, sff = TOFINEX_SIZES[size]
+    return dict(A27B, vocab_size=vocab, hidden_size=W, intermediate_size=ff, num_hidden_layers=TOFINEX_LAYERS,
+                num_attention_heads=H, num_key_value_heads=G, head_dim=d, num_experts=E, num_experts_per_tok=K,
+                moe_intermediate_size=eff, shared_expert_intermediate_size=sff, mlp_only_layers=[0],
+                norm_topk_prob=False, use_sliding_window=False, max_position_embeddings=1 << 20)
+
+
+def _tofinex_kernel_work(cfg, T, B, ctx, decode):
+    """Algorithmic bytes and floating-point operations of the design's own kernels for one step over all layers
+    (prefill of T tokens of one request, or a decode step of B requests at context ctx)."""
+    rows, W = (B if decode else T), cfg["width"]
+    out = {}
+
+    def add(name, by, fl):
+        a = out.setdefault(name, [0.0, 0.0])
+        a[0] += by
+        a[1] += fl
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        pairs = B * ctx if decode else T * (T + 1) // 2
+        by = (B * ctx * G * (d + e) * 2 + B * H * (d + e) * 2) if decode else T * (H + G) * (d + e) * 2
+        for name in (("attn_mix_tc_kernel",) if decode else ("attn_mix_tc_kernel", "pt::attn_prefill_tc_kernel")):
+            add(name, by, pairs * H * (2.0 * d + 2.0 * e))
+        # float32 rows in (and the first layer's values once more), queries out, keys and values into the cache
+        add("rope_store_kernel", rows * ((H * d + G * (d + e)) * 6 + G * e * 4), 0)
+        # a part's float32 output in, the residual read and written, its rounded copy written
+        parts = 1 if L["mlp"] is None else 2
+        add("out_norm_add_kernel", parts * rows * W * (4 + 8 + 2), 0)
+        if L["mlp"] is not None and L["mlp"]["kind"] == "moe":
+            K = L["mlp"]["router"]["top"]
+            # the experts' rows and the shared expert's row (float32) join the out_norm_add above
+            add("out_norm_add_kernel", rows * W * 4 * K, 0)
+            add("scatter_rows_scaled_kernel", rows * W * 2 * (1 + K), 0)
+    add("softcap_rows_kernel", (B if decode else 1) * cfg["vocab"] * 8, 0)
+    return out
+
+
+def _tofinex_twin_kernel_work(cfg, size, window, T, B, ctx, decode):
+    W, H, G, d, ff, E, K, eff, sff = TOFINEX_SIZES[size]
+    rows, layers = (B if decode else T), TOFINEX_LAYERS
+    if decode:
+        pairs, by = B * ctx, B * ctx * G * 2 * d * 2 + B * H * 2 * d * 2
+        attn = "attn_decode_split_kernel"
+    else:
+        pairs = T * (T + 1) // 2
+        by, attn = T * (H + G) * 2 * d * 2, "pt::attn_prefill_tc_kernel"
+    return {attn: [layers * by, layers * pairs * H * 4.0 * d],
+            "qkv_post_rows_kernel": [layers * rows * (H + 2 * G) * d * 6, 0.0],
+            # residual read and written, a part's output in, the normalised row out
+            "add_rmsnorm_vec_kernel": [(layers + 2) * rows * W * (4 + 8 + 2), 0.0],
+            "combine_add_rmsnorm_vec_kernel": [(layers - 1) * rows * W * (4 * (K + 1) + 8 + 2), 0.0],
+            "tc::gather_rows_kernel": [(layers - 1) * rows * W * 2 * (1 + K), 0.0]}
+
+
+def run_tofinex(args):
+    return _run_design(args, "tofinex", args.tofinex, 0, tofinex_config, tofinex_twin_config,
+                       _tofinex_kernel_work, _tofinex_twin_kernel_work, "moe_twin", graph_prompts=True)
+
+
 def run_reference(args):
     """The reference arm: Deyu-Kong/mini-infer itself, unmodified, built out of tree for sm_100 by
     ``baseline/build_reference.py`` and driven by ``baseline/reference_bench.cpp`` through its stock path
@@ -913,6 +999,9 @@ def main():
     ap.add_argument("--nipapel", default="", metavar="SIZES",
                     help="instead of the default workload: prefill and decode of the Nipapel design beside Qwen2-MoE at "
                          "these sizes (comma-separated, of " + ", ".join(NIPAPEL_SIZES) + "), see run_nipapel")
+    ap.add_argument("--tofinex", default="", metavar="SIZES",
+                    help="instead of the default workload: prefill and decode of the Tofinex design beside Qwen2-MoE at "
+                         "these sizes (comma-separated, of " + ", ".join(TOFINEX_SIZES) + "), see run_tofinex")
     ap.add_argument("--nipapel-window", type=int, default=1024, help="attention window of the --nipapel models")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference's program may take")
     ap.add_argument("--reference-prefill-batch", type=int, default=1,
@@ -935,6 +1024,8 @@ def main():
         return run_vizalix(args)
     if args.nipapel:
         return run_nipapel(args)
+    if args.tofinex:
+        return run_tofinex(args)
     return run_ours(args)
 
 

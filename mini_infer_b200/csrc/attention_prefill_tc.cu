@@ -82,12 +82,21 @@ struct Maps {
 // DK, DV: key and value sizes in whole 64-column halves (a key row shorter than DK reads zeros beyond its end,
 // in Q and in K alike).  hpq > 1 (with nh = nkv = 1): the heads of a query all read ONE key/value head, so the
 // rows of a tile are (query, head) pairs, hpq consecutive rows a query: q and out are [tokens * hpq, .].
-template <int DK, int DV>
+// CAPPED: every score becomes cap * tanh(score * scale / cap) before the mask and the softmax (`cap_in` =
+// scale / cap, `cap_out` = cap / scale, so that what follows scales the capped number as it scales a plain one).
+// `sink`: the softmax counts one key more, of score 0 and without a value: the reference of the exponentials
+// starts at 0 and the running sum at 1.
+__device__ __forceinline__ float fast_tanh(float x) {
+    return 1.0f - __fdividef(2.0f, fast_exp2(x * 2.8853900817779268f) + 1.0f);
+}
+
+template <int DK, int DV, bool CAPPED = false>
 __global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict__ block_table,
                        const int* __restrict__ q_start, const int* __restrict__ kv_len,
                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_pages,
-                       int window, float scale_log2, int* __restrict__ status, int keep_first, int hpq) {
+                       int window, float scale_log2, int* __restrict__ status, int keep_first, int hpq,
+                       float cap_in, float cap_out, int sink) {
     constexpr int DKH = DK / 64, DVH = DV / 64;           // 64-column halves of a key and of a value row
     constexpr uint32_t TMEM_COLS = 256;                   // S[0], S[1] (BN columns each), O (D): two blocks share an SM
     constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
@@ -256,8 +265,8 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
         const int p_row = p_lo + r / hpq;                 // position of this thread's query
         const int vis_hi = min(p_row, kvl - 1);           // last visible key
         const int vis_lo = window > 0 ? p_row - window + 1 : 0;   // first visible key
-        float m_ref = -INFINITY;                          // reference of the exponentials, in log2 units
-        float l_run = 0.f;
+        float m_ref = sink ? 0.f : -INFINITY;             // reference of the exponentials, in log2 units
+        float l_run = sink ? 1.f : 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int buf = j & 1;
@@ -272,6 +281,11 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if constexpr (CAPPED) {
+#pragma unroll
+                for (int i = 0; i < BN; ++i)
+                    v[i] = __float_as_uint(fast_tanh(__uint_as_float(v[i]) * cap_in) * cap_out);
+            }
             // does any (row, key) of this tile need the mask?
             const bool masked = (k0 + BN - 1 > p_lo) || (k0 + BN > kvl) || (window > 0 && k0 < p_hi - window + 1);
             // below a row's window only kept first keys are visible: of a tile of kept first keys those below
@@ -413,8 +427,12 @@ int mi_attn_prefill_tc_supported(int d, int page_size) {
 int mi_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                        const int* q_start, const int* kv_len, void* out, int* status, int T, int B, int max_q_len,
                        int nh, int nkv, int d, int page_size, int num_pages, int max_pages, int window, float scale,
-                       int keep_first, cudaStream_t stream) {
+                       int keep_first, float cap, int sink, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0 || T <= 0) return kOk;
+    if (cap < 0.f || !(scale > 0.f)) {
+        set_last_error("prefill attention (tcgen05): a cap of %g on scores scaled by %g", (double)cap, (double)scale);
+        return kBadShape;
+    }
     if (keep_first < 0) { set_last_error("prefill attention (tcgen05): %d kept first keys", keep_first); return kBadShape; }
     if (!mi_attn_prefill_tc_supported(d, page_size)) {
         set_last_error("prefill attention (tcgen05): head_dim %d with pages of %d tokens is not taken", d, page_size);
@@ -446,15 +464,17 @@ int mi_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
     const float scale_log2 = scale * 1.4426950408889634f;
     const int dh = d / 64;
     const size_t smem = (size_t)dh * pt::HALF_BYTES + (size_t)(pt::NK + pt::NV) * dh * pt::KV_HALF + 256;
-#define MI_PT(DD)                                                                                         \
+    const float cap_in = cap > 0.f ? scale / cap : 0.f, cap_out = cap > 0.f ? cap / scale : 0.f;
+#define MI_PT(DD, CC)                                                                                     \
     do {                                                                                                  \
-        auto kern = pt::attn_prefill_tc_kernel<DD, DD>;                                                   \
+        auto kern = pt::attn_prefill_tc_kernel<DD, DD, CC>;                                               \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
         kern<<<grid, 192, smem, stream>>>(maps, block_table, q_start, kv_len, (__nv_bfloat16*)out, nh,    \
                                           nkv, page_size, max_pages, window, scale_log2, status,          \
-                                          keep_first, 1);                                                 \
+                                          keep_first, 1, cap_in, cap_out, sink);                          \
     } while (0)
-    if (d == 64) MI_PT(64); else MI_PT(128);
+    if (cap > 0.f) { if (d == 64) MI_PT(64, true); else MI_PT(128, true); }
+    else { if (d == 64) MI_PT(64, false); else MI_PT(128, false); }
 #undef MI_PT
     return finish_launch("attn_prefill_tc");
 }
@@ -503,7 +523,8 @@ int mi_attn_prefill_tc_shared(const void* q, const void* cache, const int* block
         auto kern = pt::attn_prefill_tc_kernel<KK, VV>;                                                   \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
         kern<<<grid, 192, smem, stream>>>(maps, block_table, q_start, kv_len, (__nv_bfloat16*)out, 1, 1,  \
-                                          page_size, max_pages, window, scale_log2, status, keep_first, H); \
+                                          page_size, max_pages, window, scale_log2, status, keep_first, H,  \
+                                          0.f, 0.f, 0);                                                     \
     } while (0)
     if (dv == 64) {
         if (DKr == 64) MI_PTS(64, 64); else if (DKr == 128) MI_PTS(128, 64); else if (DKr == 192) MI_PTS(192, 64); else MI_PTS(256, 64);

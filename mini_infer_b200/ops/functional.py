@@ -353,9 +353,11 @@ def prefill_attention_tc_supported(d: int, page_size: int) -> bool:
 def prefill_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                          q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int, window: int = 0,
                          scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
-                         keep_first: int = 0) -> torch.Tensor:
+                         keep_first: int = 0, softcap: float = 0.0, sink: bool = False) -> torch.Tensor:
     """Same contract as :func:`attention`, on the tcgen05 tensor cores (TMA-fed, accumulators in
-    tensor memory): bfloat16, head sizes 64 and 128, pages of 8 to 128 tokens.  Call
+    tensor memory): bfloat16, head sizes 64 and 128, pages of 8 to 128 tokens.  ``softcap`` (0: none): every
+    scaled score becomes ``softcap * tanh(score / softcap)``; ``sink``: the softmax counts one key more, of
+    score 0 and without a value.  Call
     :func:`check_tc_status` after the step: a wait inside the kernel that ran out is reported there."""
     global _tc_pending
     _chk(q, "prefill_attention_tc q", BF16)
@@ -383,7 +385,7 @@ def prefill_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     check(library().mi_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(q_start),
                                        _ptr(kv_len), _ptr(out), _ptr(_tc_status[dev]), T, B, int(max_q_len), nh, nkv,
                                        d, page_size, num_pages, max_pages, int(window), float(scale),
-                                       int(keep_first), _stream()),
+                                       int(keep_first), float(softcap), int(bool(sink)), _stream()),
           "prefill_attention_tc")
     _tc_pending = True
     return out

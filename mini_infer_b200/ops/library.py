@@ -41,7 +41,7 @@ _SIGNATURES = {
     "mi_dense_skinny": [P, P, P, P, I, I, I, I, P],
     "mi_gather_rows_bf16": [P, P, P, I, I, P],
     "mi_attn_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
-    "mi_attn_prefill_tc": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P],
+    "mi_attn_prefill_tc": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, F, I, P],
     "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, I, F, F, P],
     "mi_grouped_gemm_tc_form": [P, P, P, P, P, I, I, I, I, I, I, I, F, F, P],
     "mi_random_fill": [P, I, L, ctypes.c_uint, ctypes.c_uint, F, F, P],

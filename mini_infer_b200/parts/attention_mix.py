@@ -7,7 +7,7 @@ head's score of a (query, key) pair becomes a mix of all heads' scores of that p
 window lets through (behind a window the first keys of a request may stay visible).  Query/key heads and value
 heads may differ in size.  One library product for q, k and v together, one kernel for head norms, rotation and
 cache write, one attention kernel that owns all heads of its queries (the mix couples them), one library product
-for the output.  Without a mix and a cap the heads are independent: prompt portions in bfloat16 then take the
+for the output.  Without a mix the heads are independent: prompt portions in bfloat16 then take the
 engine's tcgen05 attention where keys and values have one size that kernel is built for.
 
 Two further options.  ``sink``: the softmax counts one key more, whose score is 0 and which has no value,
@@ -121,8 +121,8 @@ class HeadMixAttention(Mixer):
 
         # bfloat16: scores and P.V on the tensor cores where the kernel is built for the sizes
         self._tensor_cores = rt.act == torch.bfloat16 and F.attention_mix_tc_supported(self.nh, self.nkv, self.dk, self.dv)
-        self._independent_heads = (self.mix is None and self.softcap == 0.0 and self.dk == self.dv
-                                   and not self.sink)
+        # heads that exchange nothing (a cap and one key more act on a head's own scores)
+        self._independent_heads = self.mix is None and self.dk == self.dv
         # prompt portions on the tensor-memory attention: its blocks want whole SMs (a block arrangement that
         # runs another part beside this one asks)
         self.large_steps_fill_the_device = self._tensor_cores and self._independent_heads
@@ -174,7 +174,8 @@ class HeadMixAttention(Mixer):
             # heads that exchange nothing, keys and values of one size the tcgen05 kernel is built for: prompt
             # portions (and what decodes beside them) take the engine's tensor-memory attention
             a = F.prefill_attention_tc(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
-                                       self.window, self.scale, keep_first=self.keep_first)
+                                       self.window, self.scale, keep_first=self.keep_first, softcap=self.softcap,
+                                       sink=self.sink)
         else:
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
                                    self.window, self.scale, self.softcap, keep_first=self.keep_first,

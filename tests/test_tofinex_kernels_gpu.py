@@ -88,7 +88,8 @@ def paged(k, v, page_size, num_pages, seed, dtype):
     return kc.to(dtype).to(DEV), vc.to(dtype).to(DEV), order
 
 
-def run_attention(q, k, v, scale, cap, cuts, dtype=torch.float32, page_size=8, tensor_cores=False, sink=True):
+def run_attention(q, k, v, scale, cap, cuts, dtype=torch.float32, page_size=8, tensor_cores=False, sink=True,
+                  tensor_memory=False):
     """The kernel over a hand-made paged cache, the sequence's queries cut into steps ``cuts``."""
     T, H, d = q.shape
     e = v.shape[2]
@@ -97,7 +98,11 @@ def run_attention(q, k, v, scale, cap, cuts, dtype=torch.float32, page_size=8, t
     outs, lo = [], 0
     for n in cuts:
         qq = q[lo:lo + n].to(dtype).to(DEV).contiguous()
-        if tensor_cores:
+        if tensor_memory:
+            got = F().prefill_attention_tc(qq, kc, vc, table, i32([0, n]), i32([lo + n]), n, 0, scale, softcap=cap,
+                                           sink=sink)
+            F().check_tc_status()
+        elif tensor_cores:
             kw = {}
             if n == 1:
                 splits = F().attention_mix_tc_splits(lo + 1, 0)
@@ -159,7 +164,24 @@ def test_tensor_core_attention_with_one_key_more(H, G, d, e):
     assert float((got.double() - want).abs().max()) > 2e-2 * float(want.abs().max())
 
 
-@pytest.mark.parametrize("tensor_cores", [False, True])
+@pytest.mark.parametrize("H,G,d,cap", [(4, 2, 64, 5.0), (2, 2, 128, 30.0), (6, 1, 128, 0.0), (3, 3, 64, 1.0)])
+def test_tensor_memory_attention_with_capped_scores_and_one_key_more(H, G, d, cap):
+    """Prompt portions on the tcgen05 kernel: whole, and in portions that start inside key tiles and pages."""
+    T = 450
+    g = torch.Generator().manual_seed(H + d)
+    q, k, v = (torch.randn(T, n, d, generator=g).to(torch.bfloat16).float() for n in (H, G, G))
+    want = plain_attention(q, k, v, 0.15, cap)
+    for cuts in ([T], [130, 2, 200, 17, 101]):
+        got = run_attention(q, k, v, 0.15, cap, cuts, torch.bfloat16, page_size=16, tensor_memory=True)
+        assert float((got.double() - want).abs().max()) <= 1.2e-2 * float(want.abs().max())
+    got = run_attention(q, k, v, 0.15, cap, [T], torch.bfloat16, page_size=16, tensor_memory=True, sink=False)
+    assert float((got.double() - want).abs().max()) > 2e-2 * float(want.abs().max())
+    if cap:
+        other = plain_attention(q, k, v, 0.15, 0.0)
+        assert float((other - want).abs().max()) > 2e-2 * float(want.abs().max())      # the cap matters here
+
+
+@pytest.mark.parametrize("tensor_cores", [False, True, "memory"])
 @pytest.mark.parametrize("decoded", [False, True])
 @pytest.mark.parametrize("key", [0, 1, 63, 64, 65, 255, 256, 500, 699])
 def test_a_far_key_among_hundreds_and_queries_that_match_nothing(key, decoded, tensor_cores):
@@ -167,6 +189,10 @@ def test_a_far_key_among_hundreds_and_queries_that_match_nothing(key, decoded, t
     wherever the key lies (the first tokens, page and tile borders, far back).  The query before it matches
     nothing, with scores far below zero: the added key takes all of its weight and its output is zero."""
     T, H, G, d, e = 700, 4, 2, 32, 64
+    if tensor_cores == "memory":
+        d = 64                                  # the tcgen05 kernel: keys and values of one size, portions only
+        if decoded:
+            pytest.skip("single tokens take the split kernel")
     g = torch.Generator().manual_seed(key)
     v = torch.randn(T, G, e, generator=g).to(torch.bfloat16).float()
     k = (torch.randn(T, G, d, generator=g) * 0.01).to(torch.bfloat16).float()
@@ -177,7 +203,8 @@ def test_a_far_key_among_hundreds_and_queries_that_match_nothing(key, decoded, t
     q[-2, :, 1] = -30.0                         # every score of this query is -30 * scale
     dtype = torch.bfloat16 if tensor_cores else torch.float32
     cuts = [T - 2, 1, 1] if decoded else [T]
-    got = run_attention(q, k, v, 1.0, 50.0, cuts, dtype, page_size=16, tensor_cores=tensor_cores)
+    got = run_attention(q, k, v, 1.0, 50.0, cuts, dtype, page_size=16, tensor_cores=tensor_cores is True,
+                        tensor_memory=tensor_cores == "memory")
     want = plain_attention(q, k, v, 1.0, 50.0)
     tol = 1e-2 if tensor_cores else 1e-4
     assert float((got[-1].double() - v[key].double().repeat_interleave(H // G, dim=0)).abs().max()) <= tol

@@ -91,7 +91,19 @@ CONFIG_D = {
     ],
 }
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
+# key and value heads of one size that the tensor-memory attention takes for prompt portions in bfloat16 (64 and
+# 128), beside single tokens on the split kernel
+CONFIG_E = {
+    "architecture": "Tofinex", "vocab": 192, "width": 128, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+    "logit_softcap": 30.0,
+    "layers": [
+        _layer(_attn(4, 2, 64, 64, 0.125, 30.0, {"base": 10000.0, "dims": 64}, v_mix=True), _dense(256)),
+        _layer(_attn(2, 1, 128, 128, 0.09, 4.0, {"base": 5000.0, "dims": 64}, v_mix=False), _moe(64, 8, 2, shared=128)),
+        _layer(_attn(8, 2, 64, 64, 0.2, None, {"base": 300.0, "dims": 32}, v_mix=True), _moe(128, 4, 1, shared=64)),
+    ],
+}
+
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E}
 
 
 def make_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
