@@ -836,7 +836,7 @@ def _tofinex_kernel_work(cfg, T, B, ctx, decode):
             K = L["mlp"]["router"]["top"]
             # the experts' rows and the shared expert's row (float32) join the out_norm_add above
             add("out_norm_add_kernel", rows * W * 4 * K, 0)
-            add("scatter_rows_scaled_kernel", rows * W * 2 * (1 + K), 0)
+            add("tc::gather_rows_kernel", rows * W * 2 * (1 + K), 0)
     add("softcap_rows_kernel", (B if decode else 1) * cfg["vocab"] * 8, 0)
     return out
 

@@ -229,6 +229,15 @@ __device__ __forceinline__ int decode_splits(int kvl) {
     return max(1, (kvl + SPLIT - SPLIT / 4 - 1) / SPLIT);
 }
 
+// tanh of a capped score: the library's for float32 scores; for a bfloat16 cache, whose scores carry the rounding
+// of their operands, 1 - 2 / (e^{2x} + 1) with the hardware's exponential and division (exact at both ends:
+// e^{2x} = inf gives 1, 0 gives -1).
+template <typename AT>
+__device__ __forceinline__ float capped_tanh(float x) {
+    if (sizeof(AT) == 4) return tanhf(x);
+    return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f);
+}
+
 constexpr int DEC_SPLIT = 512;      // keys per split by default; smaller splits spread one or two requests over the device
 constexpr int DEC_GROUPS = 16;
 
@@ -238,7 +247,7 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
                          const int* __restrict__ block_table, const int* __restrict__ q_start,
                          const int* __restrict__ kv_len, float* __restrict__ part_o,
                          float* __restrict__ part_ml, int nh, int nkv, int page_size, int max_pages,
-                         int max_splits, int window, float scale) {
+                         int max_splits, int window, float scale, float cap) {
     constexpr int E = D / 8;  // elements per thread
     wait_for_earlier_kernels();
     const int b = blockIdx.z, h = blockIdx.y, sp = blockIdx.x;
@@ -261,6 +270,7 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
 #pragma unroll
     for (int i = 0; i < E; ++i) qr[i] *= scale;
     float m_run = -INFINITY, l_run = 0.f;
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
     float acc[E];
 #pragma unroll
     for (int i = 0; i < E; ++i) acc[i] = 0.f;
@@ -305,6 +315,7 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
             for (int i = 0; i < E; ++i) dot += qr[i] * kf[i];
 #pragma unroll
             for (int o = 4; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o);
+            if (cap > 0.f) dot = cap * capped_tanh<AT>(dot * inv_cap);
             const float m_new = fmaxf(m_run, dot);
             const float alpha = expf(m_run - m_new);
             const float p = expf(dot - m_new);
@@ -352,7 +363,7 @@ constexpr int MERGE_CAP = 512;
 template <typename AT, int D, int SPLIT>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const int* __restrict__ q_start, const int* __restrict__ kv_len,
-                                         AT* __restrict__ out, int nh, int max_splits, int window) {
+                                         AT* __restrict__ out, int nh, int max_splits, int window, int sink) {
     __shared__ float sm_w[MERGE_CAP], sm_l[MERGE_CAP], sm_red[4];
     wait_for_earlier_kernels();
     const int b = blockIdx.y, h = blockIdx.x;
@@ -379,12 +390,14 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
         __syncthreads();
         float m_all = -INFINITY;
         for (int w = 0; w < (int)(blockDim.x + 31) / 32; ++w) m_all = fmaxf(m_all, sm_red[w]);
+        // one key more, of score 0 and without a value: it joins the reference and the sum, not the rows
+        if (sink) m_all = fmaxf(m_all, 0.f);
         for (int s = threadIdx.x; s < n; s += blockDim.x) {
             const float m = sm_w[s];
             sm_w[s] = m == -INFINITY ? 0.f : expf(m - m_all);
         }
         __syncthreads();
-        float l = 0.f;
+        float l = sink ? expf(-m_all) : 0.f;
         for (int s = 0; s < n; ++s) l += sm_w[s] * sm_l[s];
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const float* po = part_o + (base + first_split) * D;
@@ -398,7 +411,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
     }
     float m_all = -INFINITY;
     for (int s = first_split; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(base + s) * 2]);
-    float l = 0.f;
+    if (sink) m_all = fmaxf(m_all, 0.f);
+    float l = sink ? expf(-m_all) : 0.f;
     for (int s = first_split; s < n_splits; ++s) {
         const float m = part_ml[(base + s) * 2];
         l += (m == -INFINITY ? 0.f : expf(m - m_all)) * part_ml[(base + s) * 2 + 1];
@@ -479,11 +493,15 @@ int mi_attn_decode_split_supported(int split) { return (split == 128 || split ==
 
 // Decode attention: every request has exactly one query token.  `part_o` needs
 // B*nh*max_splits*d floats, `part_ml` B*nh*max_splits*2, with max_splits >= ceil(max_kv_len / split).
-int mi_attn_decode_split(const void* q, const void* k_cache, const void* v_cache, int adtype, const int* block_table,
-                         const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
-                         int nh, int nkv, int d, int page_size, int max_pages, int max_splits, int split, int window,
-                         float scale, cudaStream_t stream) {
+// cap > 0: every scaled score becomes cap * tanh(score / cap); sink: the softmax counts one key more, of score
+// 0 and without a value.
+int mi_attn_decode_split_form(const void* q, const void* k_cache, const void* v_cache, int adtype,
+                              const int* block_table, const int* q_start, const int* kv_len, void* out,
+                              float* part_o, float* part_ml, int B, int nh, int nkv, int d, int page_size,
+                              int max_pages, int max_splits, int split, int window, float scale, float cap, int sink,
+                              cudaStream_t stream) {
     if (B <= 0) return kOk;
+    if (cap < 0.f) { set_last_error("decode attention: a cap of %g", (double)cap); return kBadShape; }
     if (!mi_attn_decode_supported(d)) {
         set_last_error("decode attention: head_dim %d is not built (64, 128, 256)", d);
         return kBadShape;
@@ -506,9 +524,9 @@ int mi_attn_decode_split(const void* q, const void* k_cache, const void* v_cache
     do {                                                                                                  \
         launch_dependent(attn_decode_split_kernel<AT, DD, SS>, grid, dim3(128), 0, stream,                \
             (const AT*)q, (const AT*)k_cache, (const AT*)v_cache, block_table, q_start, kv_len, part_o,  \
-            part_ml, nh, nkv, page_size, max_pages, max_splits, window, scale);                           \
+            part_ml, nh, nkv, page_size, max_pages, max_splits, window, scale, cap);                      \
         launch_dependent(attn_decode_merge_kernel<AT, DD, SS>, mgrid, dim3(DD <= 128 ? DD : 128), 0, stream, \
-            part_o, part_ml, q_start, kv_len, (AT*)out, nh, max_splits, window);                          \
+            part_o, part_ml, q_start, kv_len, (AT*)out, nh, max_splits, window, sink);                    \
     } while (0)
 #define MI_DEC_D(SS) do { if (d == 64) MI_DEC(64, SS); else if (d == 128) MI_DEC(128, SS); else MI_DEC(256, SS); } while (0)
     MI_DISPATCH_1(adtype, AT,
@@ -516,6 +534,15 @@ int mi_attn_decode_split(const void* q, const void* k_cache, const void* v_cache
 #undef MI_DEC_D
 #undef MI_DEC
     return finish_launch("attn_decode", 2);
+}
+
+int mi_attn_decode_split(const void* q, const void* k_cache, const void* v_cache, int adtype, const int* block_table,
+                         const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
+                         int nh, int nkv, int d, int page_size, int max_pages, int max_splits, int split, int window,
+                         float scale, cudaStream_t stream) {
+    return mi_attn_decode_split_form(q, k_cache, v_cache, adtype, block_table, q_start, kv_len, out, part_o, part_ml,
+                                     B, nh, nkv, d, page_size, max_pages, max_splits, split, window, scale, 0.f, 0,
+                                     stream);
 }
 
 // The same with the default split size.

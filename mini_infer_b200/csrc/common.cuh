@@ -49,8 +49,13 @@ __device__ __forceinline__ float clamped_glu_f(float gate, float up, float limit
 }
 
 // How the two halves of a gated unit meet in a product's epilogue: kind 0 silu(gate) * up, kind 1 the
-// bounded form above.
-struct GluForm { int kind; float limit; float slope; };
+// bounded form above.  `row_scale` (or null): one number per row of the product's RESULT that multiplies both
+// halves before they meet, glu(s gate, s up): a product is linear in its input, so this is the gated unit of
+// the row s * x without a scaled copy of x (an expert whose weight multiplies what it reads).
+struct GluForm { int kind; float limit; float slope; const float* row_scale; };
+__device__ __forceinline__ float glu_row_scale(const GluForm& f, int64_t row) {
+    return f.row_scale ? __ldg(f.row_scale + row) : 1.0f;
+}
 __device__ __forceinline__ float glu_join(float gate, float up, GluForm f) {
     return f.kind == 1 ? clamped_glu_f(gate, up, f.limit, f.slope) : gate / (1.0f + expf(-gate)) * up;
 }

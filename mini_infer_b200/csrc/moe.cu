@@ -415,17 +415,13 @@ moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restr
                         norm_topk, bias);
 }
 
-// out[dest[i]] = w[i] * x[i / K] for every (token, slot) pair i: the rows of an expert block whose weights
-// scale the experts' INPUTS, laid out in expert order.  One block per pair.
-template <typename AT>
-__global__ void __launch_bounds__(128)
-scatter_rows_scaled_kernel(const AT* __restrict__ x, const int* __restrict__ dest, const float* __restrict__ w,
-                           AT* __restrict__ out, int K, int H) {
+// out[dest[i]] = v[i]: one number per (token, slot) pair brought into expert order (the weights of an expert
+// block that scale the experts' INPUTS reach the grouped products' epilogues as one number per sorted row).
+__global__ void __launch_bounds__(256)
+scatter_values_kernel(const float* __restrict__ v, const int* __restrict__ dest, float* __restrict__ out, int n) {
     wait_for_earlier_kernels();
-    const int64_t i = blockIdx.x;
-    const int64_t t = i / K, r = dest ? dest[i] : i;
-    const float wi = w[i];
-    for (int c = threadIdx.x; c < H; c += blockDim.x) out[r * H + c] = from_float<AT>(wi * to_float(x[t * H + c]));
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[dest[i]] = v[i];
 }
 
 // ---------------------------------------------------------------------------
@@ -810,7 +806,10 @@ grouped_gemm_plain_kernel(const AT* __restrict__ A, const int* __restrict__ gath
             const int r = ty * 4 + i;
             if (r < rows) {
                 float v = acc[i];
-                if (MODE == 1) v = glu_join(v, acu[i], glu);
+                if (MODE == 1) {
+                    const float s = glu_row_scale(glu, row0 + r);
+                    v = glu_join(v * s, acu[i] * s, glu);
+                }
                 C[(int64_t)(row0 + r) * Nout + n] = from_float<CT>(v);
             }
         }
@@ -1009,14 +1008,11 @@ int mi_moe_norm_route_small(float* hidden, const float* delta, const void* norm_
 }
 
 // `counts_scratch` is not used any more (the signature is kept).
-int mi_scatter_rows_scaled(const void* x, const int* dest, const float* w, void* out, int adtype, int n_pairs, int K,
-                           int H, cudaStream_t stream) {
-    if (n_pairs <= 0 || H <= 0) return kOk;
-    if (K < 1 || !w) { set_last_error("scatter_rows_scaled: %d slots per token, weights %p", K, (const void*)w); return kBadShape; }
-    MI_DISPATCH_1(adtype, AT,
-        launch_dependent(scatter_rows_scaled_kernel<AT>, dim3(n_pairs), dim3(128), 0, stream, (const AT*)x, dest, w,
-                         (AT*)out, K, H));
-    return finish_launch("scatter_rows_scaled");
+int mi_scatter_values(const float* v, const int* dest, float* out, int n, cudaStream_t stream) {
+    if (n <= 0) return kOk;
+    if (!v || !dest || !out) { set_last_error("scatter_values: a null operand"); return kBadShape; }
+    launch_dependent(scatter_values_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, v, dest, out, n);
+    return finish_launch("scatter_values");
 }
 
 int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* inv_perm, int* counts_scratch, int T,
@@ -1047,9 +1043,10 @@ int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* in
 // cdtype: type of C (0 float, 1 bfloat16).  mode 1 = SwiGLU pair (W holds 2*Nout rows per expert).
 int mi_grouped_gemm_plain(const void* A, int adtype, const int* gather, const void* W, int wdtype,
                           const int* offsets, void* C, int cdtype, int n_rows, int E, int Nout, int Kd,
-                          int mode, int glu_kind, float glu_limit, float glu_slope, cudaStream_t stream) {
+                          int mode, int glu_kind, float glu_limit, float glu_slope, const float* row_scale,
+                          cudaStream_t stream) {
     if (n_rows <= 0) return kOk;
-    const GluForm glu{glu_kind, glu_limit, glu_slope};
+    const GluForm glu{glu_kind, glu_limit, glu_slope, mode == 1 ? row_scale : nullptr};
     const int max_tiles = (n_rows + GB - 1) / GB + E;
     if (max_tiles > 65535) {
         set_last_error("grouped product: %d row tiles exceed the grid limit", max_tiles);

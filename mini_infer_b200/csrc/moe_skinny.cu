@@ -87,10 +87,12 @@ __device__ __forceinline__ void skinny_pass(const __nv_bfloat16* __restrict__ A,
             const int f = f0 + g + ((i & 2) ? 8 : 0);
             const int r = 8 * j + 2 * t + (i & 1);
             if (f < Nout && r < rows) {
-                const int64_t o = (int64_t)(dst ? dst[r] : row0 + r) * Nout + f;
+                const int64_t orow = dst ? dst[r] : row0 + r;
+                const int64_t o = orow * Nout + f;
                 if (MODE == 1) {
-                    const float gv = acc[j][0][i];
-                    reinterpret_cast<__nv_bfloat16*>(C)[o] = __float2bfloat16_rn(glu_join(gv, acc[j][1][i], glu));
+                    const float s = glu_row_scale(glu, orow);
+                    const float gv = acc[j][0][i] * s;
+                    reinterpret_cast<__nv_bfloat16*>(C)[o] = __float2bfloat16_rn(glu_join(gv, acc[j][1][i] * s, glu));
                 } else {
                     reinterpret_cast<float*>(C)[o] = acc[j][0][i];
                 }
@@ -246,10 +248,12 @@ __device__ __forceinline__ void splitk_tile(const __nv_bfloat16* __restrict__ A,
             if (MODE == 1) s1 += red[w][(j * H + H - 1) * 4 + i][l];
         }
         if (f < Nout && r < rows) {
-            const int64_t at = (int64_t)(dst ? dst[r] : r) * Nout + f;
+            const int64_t orow = dst ? dst[r] : r;
+            const int64_t at = orow * Nout + f;
             if (MODE == 1) {
                 if (bias) { s0 += bias[f]; s1 += bias[Nout + f]; }
-                reinterpret_cast<__nv_bfloat16*>(C)[at] = __float2bfloat16_rn(glu_join(s0, s1, glu));
+                const float rs = glu_row_scale(glu, orow);
+                reinterpret_cast<__nv_bfloat16*>(C)[at] = __float2bfloat16_rn(glu_join(s0 * rs, s1 * rs, glu));
             } else {
                 if (bias) s0 += bias[f];
                 reinterpret_cast<float*>(C)[at] = s0;
@@ -437,8 +441,8 @@ int mi_grouped_gemm_skinny_supported(int Kd) { return (Kd > 0 && Kd % 32 == 0) ?
 // A, W bfloat16; C bfloat16 for mode 1 (SwiGLU pair, W holds 2*Nout rows per expert), float for mode 0.
 int mi_grouped_gemm_skinny(const void* A, const int* gather, const void* W, const int* offsets, void* C,
                            int E, int Nout, int Kd, int mode, int glu_kind, float glu_limit, float glu_slope,
-                           cudaStream_t stream) {
-    const GluForm glu{glu_kind, glu_limit, glu_slope};
+                           const float* row_scale, cudaStream_t stream) {
+    const GluForm glu{glu_kind, glu_limit, glu_slope, mode == 1 ? row_scale : nullptr};
     if (!mi_grouped_gemm_skinny_supported(Kd)) {
         set_last_error("grouped product (decode): inner size %d is not a multiple of 32", Kd);
         return kBadShape;
@@ -468,8 +472,8 @@ int mi_grouped_gemm_skinny_pairs_split_inner_max_tokens() { return PAIR_SPLITK_M
 // token t's row under the pair's expert; mode 0: A [T*K, Kd] indexed by pair, C float [T*K, Nout].
 int mi_grouped_gemm_skinny_pairs(const void* A, const int* topk_idx, const void* W, void* C, int T, int K, int E,
                                  int Nout, int Kd, int mode, int glu_kind, float glu_limit, float glu_slope,
-                                 cudaStream_t stream) {
-    const GluForm glu{glu_kind, glu_limit, glu_slope};
+                                 const float* row_scale, cudaStream_t stream) {
+    const GluForm glu{glu_kind, glu_limit, glu_slope, mode == 1 ? row_scale : nullptr};
     if (!mi_grouped_gemm_skinny_supported(Kd)) {
         set_last_error("grouped product (decode): inner size %d is not a multiple of 32", Kd);
         return kBadShape;

@@ -177,10 +177,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             if (c0 + i < rows) {
-                                const float gv = __uint_as_float(g[i]);
+                                const float rs = glu_row_scale(glu, row0 + c0 + i);
+                                const float gv = __uint_as_float(g[i]) * rs;
                                 // the result is rounded to bfloat16: the fast exponential and division are exact enough
                                 const __nv_bfloat16 v =
-                                    __float2bfloat16_rn(glu_join_fast(gv, __uint_as_float(u[i]), glu));
+                                    __float2bfloat16_rn(glu_join_fast(gv, __uint_as_float(u[i]) * rs, glu));
                                 if (staged) st[(size_t)i * BF] = v;
                                 else if (f < Nout) out[(int64_t)i * Nout] = v;
                             }
@@ -412,10 +413,12 @@ grouped_gemm_tc_persistent_kernel(const __grid_constant__ RowMaps maps_a, const 
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            const float gv = __uint_as_float(g[j]);
+                            // (rows beyond the tile's last hold nothing and are not stored)
+                            const float rs = c0 + j < rows ? glu_row_scale(glu, row0 + c0 + j) : 1.0f;
+                            const float gv = __uint_as_float(g[j]) * rs;
                             // the result is rounded to bfloat16: the fast exponential and division are exact enough
                             g[j] = (uint32_t)__bfloat16_as_ushort(
-                                __float2bfloat16_rn(glu_join_fast(gv, __uint_as_float(u[j]), glu)));
+                                __float2bfloat16_rn(glu_join_fast(gv, __uint_as_float(u[j]) * rs, glu)));
                         }
                     } else {
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -525,16 +528,17 @@ void mi_grouped_gemm_tc_test_fault(int skip_kb, unsigned int wait_limit) {
 
 // A: [n_rows, Kd] bfloat16, rows sorted by expert (offsets[E+1]); W: [E, wrows, Kd] bfloat16.
 // mode 1: C bfloat16 [n_rows, Nout] = glu(gate, up) with W holding 2*Nout rows per expert (glu_kind 0:
-// silu(gate) * up; 1: the bounded form of common.cuh with glu_limit and glu_slope);
+// silu(gate) * up; 1: the bounded form of common.cuh with glu_limit and glu_slope; row_scale, or null: one
+// number per result row that multiplies both halves before they meet);
 // mode 0: C float [n_rows, Nout].  `status` (device int, zero before the first call) receives a
 // non-zero code if a wait inside the kernel ran out.
 // form: -1 chooses; 0 / 1 one block per tile with row tiles of 128 (two blocks per SM) / 256;
 //       2 / 3 persistent with row tiles of 160 and four pipeline stages / 256 and three.
 int mi_grouped_gemm_tc_form(const void* A, const void* W, const int* offsets, void* C, int* status, int n_rows,
                             int E, int Nout, int Kd, int mode, int form, int glu_kind, float glu_limit,
-                            float glu_slope, cudaStream_t stream) {
+                            float glu_slope, const float* row_scale, cudaStream_t stream) {
     if (n_rows <= 0) return kOk;
-    const GluForm glu{glu_kind, glu_limit, glu_slope};
+    const GluForm glu{glu_kind, glu_limit, glu_slope, mode == 1 ? row_scale : nullptr};
     if (!mi_grouped_gemm_tc_supported(Kd)) {
         set_last_error("grouped product (tensor cores): inner size %d is not a multiple of %d", Kd, tc::BK);
         return kBadShape;
@@ -631,9 +635,9 @@ int mi_grouped_gemm_tc_form(const void* A, const void* W, const int* offsets, vo
 
 int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C, int* status, int n_rows, int E,
                        int Nout, int Kd, int mode, int glu_kind, float glu_limit, float glu_slope,
-                       cudaStream_t stream) {
+                       const float* row_scale, cudaStream_t stream) {
     return mi_grouped_gemm_tc_form(A, W, offsets, C, status, n_rows, E, Nout, Kd, mode, -1, glu_kind, glu_limit,
-                                   glu_slope, stream);
+                                   glu_slope, row_scale, stream);
 }
 
 }  // extern "C"

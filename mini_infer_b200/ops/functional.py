@@ -442,8 +442,11 @@ DECODE_SPLIT_SIZES = (128, 256, 512)      # the split sizes the decode attention
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                      q_start: torch.Tensor, kv_len: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                      max_splits: int, window: int = 0, scale: Optional[float] = None,
-                     out: Optional[torch.Tensor] = None, split: Optional[int] = None) -> torch.Tensor:
-    """Split-KV attention when every request brings exactly one token.
+                     out: Optional[torch.Tensor] = None, split: Optional[int] = None, softcap: float = 0.0,
+                     sink: bool = False) -> torch.Tensor:
+    """Split-KV attention when every request brings exactly one token.  ``softcap`` (0: none): every scaled
+    score becomes ``softcap * tanh(score / softcap)``; ``sink``: the softmax counts one key more, of score 0
+    and without a value.
 
     ``part_o`` (``>= B*nh*max_splits*d`` floats) and ``part_ml`` (``>= B*nh*max_splits*2``)
     are scratch; ``max_splits >= ceil(longest kv_len / split)`` with ``split`` keys per split
@@ -479,10 +482,11 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         longest = int(kv_len.max())
         if max_splits * int(split) < longest - int(split) // 4:
             _bad("decode_attention", f"{max_splits} splits of {split} keys cannot hold the longest request ({longest})")
-    check(library().mi_attn_decode_split(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "decode_attention q"),
-                                         _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), _ptr(part_o),
-                                         _ptr(part_ml), B, nh, nkv, d, page_size, max_pages, int(max_splits),
-                                         int(split), int(window), float(scale), _stream()), "decode_attention")
+    check(library().mi_attn_decode_split_form(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "decode_attention q"),
+                                              _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), _ptr(part_o),
+                                              _ptr(part_ml), B, nh, nkv, d, page_size, max_pages, int(max_splits),
+                                              int(split), int(window), float(scale), float(softcap), int(bool(sink)),
+                                              _stream()), "decode_attention")
     return out
 
 
@@ -635,13 +639,16 @@ def _glu_args(glu) -> Tuple[int, float, float]:
 
 
 def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,
-                       n_rows: int, swiglu_pair: bool, out_dtype: torch.dtype, glu=None) -> torch.Tensor:
+                       n_rows: int, swiglu_pair: bool, out_dtype: torch.dtype, glu=None,
+                       row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Per-expert product of sorted rows (float arithmetic).
 
     ``w`` is ``[E, Nout, K]`` or, with ``swiglu_pair``, ``[E, 2*Nout, K]`` (gate rows,
     then up rows) and the result is ``silu(gate) * up`` (or the bounded form that ``glu`` names,
     :func:`_glu_args`).  Row ``r`` of the result
-    uses ``a[gather[r]]`` (or ``a[r]``) and the expert whose offset range holds ``r``.
+    uses ``a[gather[r]]`` (or ``a[r]``) and the expert whose offset range holds ``r``.  ``row_scale``
+    (float32, one number per result row, paired products only): both halves are multiplied by the row's number
+    before they meet, which is the gated unit of the scaled input row.
     """
     _chk(a, "grouped_gemm a")
     Kd = a.shape[1]
@@ -659,7 +666,9 @@ def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch
     check(library().mi_grouped_gemm_plain(_ptr(a), _code(a, "grouped_gemm a"), _ptr(gather), _ptr(w),
                                           _code(w, "grouped_gemm w"), _ptr(offsets), _ptr(out),
                                           _code(out, "grouped_gemm out"), int(n_rows), E, nout, Kd,
-                                          1 if swiglu_pair else 0, *_glu_args(glu), _stream()), "grouped_gemm_plain")
+                                          1 if swiglu_pair else 0, *_glu_args(glu),
+                                          _row_scale(row_scale, int(n_rows), swiglu_pair, "grouped_gemm_plain"),
+                                          _stream()), "grouped_gemm_plain")
     return out
 
 
@@ -708,7 +717,8 @@ def grouped_gemm_skinny_supported(kd: int) -> bool:
 
 
 def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,
-                        n_rows: int, swiglu_pair: bool, glu=None) -> torch.Tensor:
+                        n_rows: int, swiglu_pair: bool, glu=None,
+                        row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The grouped product for a few rows per expert (decode), bfloat16 on tensor cores.
 
     Same contract as :func:`grouped_gemm_plain`; the result is bfloat16 with ``swiglu_pair``
@@ -728,7 +738,9 @@ def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torc
         if gather is None and a.shape[0] < n_rows:
             _bad("grouped_gemm_skinny", f"{n_rows} rows wanted, the input has {a.shape[0]}")
     check(library().mi_grouped_gemm_skinny(_ptr(a), _ptr(gather), _ptr(w), _ptr(offsets), _ptr(out), E, nout, Kd,
-                                           1 if swiglu_pair else 0, *_glu_args(glu), _stream()), "grouped_gemm_skinny")
+                                           1 if swiglu_pair else 0, *_glu_args(glu),
+                                           _row_scale(row_scale, int(n_rows), swiglu_pair, "grouped_gemm_skinny"),
+                                           _stream()), "grouped_gemm_skinny")
     return out
 
 
@@ -809,7 +821,7 @@ def skinny_pairs_split_inner_max_tokens() -> int:
 
 
 def grouped_gemm_skinny_pairs(a: torch.Tensor, topk_idx: torch.Tensor, w: torch.Tensor,
-                              swiglu_pair: bool, glu=None) -> torch.Tensor:
+                              swiglu_pair: bool, glu=None, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The decode-sized grouped product without a permutation: row ``t*K + k`` of the result
     belongs to the pair (token t, slot k) and is computed under expert ``topk_idx[t, k]``.
 
@@ -828,7 +840,9 @@ def grouped_gemm_skinny_pairs(a: torch.Tensor, topk_idx: torch.Tensor, w: torch.
     if DEBUG_BOUNDS:
         _dbg_range(topk_idx, 0, E, "grouped_gemm_skinny_pairs expert indices")
     check(library().mi_grouped_gemm_skinny_pairs(_ptr(a), _ptr(topk_idx), _ptr(w), _ptr(out), T, K, E, nout, Kd,
-                                                 1 if swiglu_pair else 0, *_glu_args(glu), _stream()),
+                                                 1 if swiglu_pair else 0, *_glu_args(glu),
+                                                 _row_scale(row_scale, T * K, swiglu_pair, "grouped_gemm_skinny_pairs"),
+                                                 _stream()),
           "grouped_gemm_skinny_pairs")
     return out
 
@@ -851,23 +865,31 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def scatter_rows_scaled(x: torch.Tensor, dest: Optional[torch.Tensor], weights: torch.Tensor) -> torch.Tensor:
-    """``out[dest[t * K + k]] = weights[t, k] * x[t]`` (``dest`` None: row ``t * K + k``): the inputs of an expert
-    block whose weights scale what the experts read, laid out in expert order.  The product is formed in float32
-    and rounded once to the type of ``x``."""
-    _chk(x, "scatter_rows_scaled x")
-    T, H = x.shape
-    _chk(weights, "scatter_rows_scaled weights", F32, (T, None))
-    K = weights.shape[1]
-    _chk(dest, "scatter_rows_scaled dest", I32)
-    if dest is not None and dest.numel() != T * K:
-        raise ValueError(f"scatter_rows_scaled: {dest.numel()} places for {T * K} (token, slot) pairs")
-    out = torch.empty(T * K, H, dtype=x.dtype, device=x.device)
+def scatter_values(values: torch.Tensor, dest: torch.Tensor) -> torch.Tensor:
+    """``out[dest[i]] = values[i]`` over the flattened operands (float32 values, int32 places that are a
+    permutation): one number per (token, slot) pair brought into expert order."""
+    _chk(values, "scatter_values values", F32)
+    _chk(dest, "scatter_values dest", I32)
+    n = values.numel()
+    if dest.numel() != n:
+        raise ValueError(f"scatter_values: {dest.numel()} places for {n} values")
+    out = torch.empty(n, dtype=F32, device=values.device)
     if DEBUG_BOUNDS:
-        _dbg_range(dest, 0, T * K, "scatter_rows_scaled dest")
-    check(library().mi_scatter_rows_scaled(_ptr(x), _ptr(dest), _ptr(weights), _ptr(out), _code(x, "scatter_rows_scaled x"),
-                                           T * K, K, H, _stream()), "scatter_rows_scaled")
+        _dbg_range(dest, 0, n, "scatter_values dest")
+    check(library().mi_scatter_values(_ptr(values), _ptr(dest), _ptr(out), n, _stream()), "scatter_values")
     return out
+
+
+def _row_scale(row_scale: Optional[torch.Tensor], rows: int, swiglu_pair: bool, what: str):
+    """Pointer of the optional float32 number per result row that scales both halves of a gated unit."""
+    if row_scale is None:
+        return None
+    if not swiglu_pair:
+        raise ValueError(f"{what}: a scale per row belongs to a paired product's gated units")
+    _chk(row_scale, what + " row_scale", F32)
+    if row_scale.numel() != rows:
+        raise ValueError(f"{what}: {row_scale.numel()} row scales for {rows} rows")
+    return _ptr(row_scale)
 
 
 _tc_status = {}
@@ -878,7 +900,7 @@ TC_FORMS = (0, 1, 2, 3)
 
 
 def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, swiglu_pair: bool,
-                    form: Optional[int] = None, glu=None) -> torch.Tensor:
+                    form: Optional[int] = None, glu=None, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The grouped product for many rows per expert (prefill): tcgen05 tensor cores fed by TMA.
 
     ``a_sorted [N, K]`` holds the rows already in expert order.  Result as for
@@ -902,7 +924,8 @@ def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tens
         _dbg_offsets(offsets, int(n_rows), "grouped_gemm_tc")
     check(library().mi_grouped_gemm_tc_form(_ptr(a_sorted), _ptr(w), _ptr(offsets), _ptr(out), _ptr(_tc_status[dev]),
                                             n_rows, E, nout, Kd, 1 if swiglu_pair else 0,
-                                            -1 if form is None else int(form), *_glu_args(glu), _stream()),
+                                            -1 if form is None else int(form), *_glu_args(glu),
+                                            _row_scale(row_scale, n_rows, swiglu_pair, "grouped_gemm_tc"), _stream()),
           "grouped_gemm_tc")
     _tc_pending = True
     return out

@@ -29,21 +29,22 @@ _SIGNATURES = {
     "mi_attn_tiled": [P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_decode": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_decode_split": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
+    "mi_attn_decode_split_form": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, P],
     "mi_moe_router": [P, I, P, P, I, P, P, P, P, P, I, I, I, I, I, P, P],
     "mi_moe_permute": [P, P, P, P, P, I, I, I, P],
-    "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, I, F, F, P],
+    "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, I, F, F, P, P],
     "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
-    "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, I, F, F, P],
+    "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, I, F, F, P, P],
     "mi_moe_route_small": [P, I, P, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
     "mi_moe_norm_route_small": [P, P, P, I, F, P, I, P, P, I, P, P, P, P, I, I, I, I, I, P],
-    "mi_grouped_gemm_skinny_pairs": [P, P, P, P, I, I, I, I, I, I, I, F, F, P],
+    "mi_grouped_gemm_skinny_pairs": [P, P, P, P, I, I, I, I, I, I, I, F, F, P, P],
     "mi_qkv_skinny": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "mi_dense_skinny": [P, P, P, P, I, I, I, I, P],
     "mi_gather_rows_bf16": [P, P, P, I, I, P],
     "mi_attn_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_prefill_tc": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, F, I, P],
-    "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, I, F, F, P],
-    "mi_grouped_gemm_tc_form": [P, P, P, P, P, I, I, I, I, I, I, I, F, F, P],
+    "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, I, F, F, P, P],
+    "mi_grouped_gemm_tc_form": [P, P, P, P, P, I, I, I, I, I, I, I, F, F, P, P],
     "mi_random_fill": [P, I, L, ctypes.c_uint, ctypes.c_uint, F, F, P],
     "mi_dense_f32": [P, P, P, I, I, I, P],
     "mi_l2_prefetch": [P, ctypes.c_ulonglong, P],
@@ -57,7 +58,7 @@ _SIGNATURES = {
     "mi_out_norm_add": [P, P, P, P, P, P, P, I, P, I, P, I, I, I, F, F, P],
     "mi_softcap_rows": [P, L, F, P],
     "mi_cast_rows": [P, P, I, L, P],
-    "mi_scatter_rows_scaled": [P, P, P, P, I, I, I, I, P],
+    "mi_scatter_values": [P, P, P, I, P],
     "mi_add2_rmsnorm_scalar": [P, P, P, P, P, P, P, P, I, I, I, F, P],
     "mi_geglu_tanh": [P, P, I, L, I, P],
     "mi_concat_cast": [P, P, P, P, P, I, I, I, P],

@@ -7,8 +7,9 @@ head's score of a (query, key) pair becomes a mix of all heads' scores of that p
 window lets through (behind a window the first keys of a request may stay visible).  Query/key heads and value
 heads may differ in size.  One library product for q, k and v together, one kernel for head norms, rotation and
 cache write, one attention kernel that owns all heads of its queries (the mix couples them), one library product
-for the output.  Without a mix the heads are independent: prompt portions in bfloat16 then take the
-engine's tcgen05 attention where keys and values have one size that kernel is built for.
+for the output.  Without a mix the heads are independent: in bfloat16, where keys and values have one size that
+those kernels are built for, prompt portions then take the engine's tcgen05 attention and steps of single tokens
+its split-KV kernel (both know the cap and the added key).
 
 Two further options.  ``sink``: the softmax counts one key more, whose score is 0 and which has no value,
 ``p_j = exp(s_j) / (1 + sum exp(s_j))``, so a query may give its weight to nothing.  ``value_blend``: the layers
@@ -27,6 +28,7 @@ from ..config.registry import part_class, register_part
 from ..config.spec import PartSpec
 from ..ops import functional as F
 from .base import CacheBinding, KVNeed, Mixer, Runtime, StepContext, TensorDecl, linear
+from .tuning import TUNING
 
 
 class HeadMixAttention(Mixer):
@@ -65,6 +67,9 @@ class HeadMixAttention(Mixer):
         self.softcap = float(p.get("softcap", 0.0) or 0.0)
         self.head_mix = bool(p.get("head_mix", False))
         self.sink = bool(p.get("sink", False))
+        if not self.head_mix and self.dk == self.dv:
+            # independent heads of one size may decode on the engine's split-KV kernel
+            self.kernel_files = type(self).kernel_files + ("attention.cu",)
         self.blend = dict(p["value_blend"]) if p.get("value_blend") else None
         if self.blend is not None:
             self.blend_key = "value_blend:" + str(self.blend["name"])
@@ -126,6 +131,10 @@ class HeadMixAttention(Mixer):
         # prompt portions on the tensor-memory attention: its blocks want whole SMs (a block arrangement that
         # runs another part beside this one asks)
         self.large_steps_fill_the_device = self._tensor_cores and self._independent_heads
+        # single tokens of independent heads in bfloat16: the engine's split-KV kernel where it is built for
+        # the head size (it reads keys and values once per head at the memory's speed and keeps no first keys)
+        self._split_decode = (rt.act == torch.bfloat16 and self._independent_heads and self.keep_first == 0
+                              and F.decode_attention_supported(self.dk))
 
     def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
         F.l2_prefetch(self.w_qkv)
@@ -139,8 +148,13 @@ class HeadMixAttention(Mixer):
 
     def scratch_need(self, max_requests: int, max_context: int) -> Dict[str, int]:
         splits = F.attention_mix_tc_splits(self._span(max_context), self.keep_first)
-        return {"attn_mix_part_o": max_requests * splits * self.nh * self.dv,
+        need = {"attn_mix_part_o": max_requests * splits * self.nh * self.dv,
                 "attn_mix_part_ml": max_requests * splits * self.nh * 2}
+        if self.dk == self.dv and F.decode_attention_supported(self.dk):
+            splits = -(-max_context // min(F.DECODE_SPLIT_SIZES))
+            need.update({"attn_part_o": max_requests * self.nh * splits * self.dk,
+                         "attn_part_ml": max_requests * self.nh * splits * 2})
+        return need
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         view = ctx.kv_groups[cache.group]
@@ -164,6 +178,12 @@ class HeadMixAttention(Mixer):
             # float32: one kernel for every step, sums in an order that the cut of the step cannot change
             a = F.attention_mix(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
                                 self.window, self.scale, self.softcap, self.keep_first, sink=self.sink)
+        elif ctx.all_decode and self._split_decode and "attn_part_o" in ctx.scratch:
+            # one or two requests alone cannot fill the device with splits of 512 keys
+            split = TUNING.decode_split(ctx.num_requests, F.decode_split_size())
+            a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.scratch["attn_part_o"],
+                                   ctx.scratch["attn_part_ml"], -(-ctx.max_kv_len // split), self.window,
+                                   scale=self.scale, split=split, softcap=self.softcap, sink=self.sink)
         elif ctx.all_decode and "attn_mix_part_o" in ctx.scratch:
             # one token per request: a block per request could not pull a window of keys fast enough
             splits = F.attention_mix_tc_splits(self._span(ctx.max_kv_len), self.keep_first)

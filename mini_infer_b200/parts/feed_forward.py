@@ -115,7 +115,9 @@ class SparseMoE(FeedForward):
     logits before the choice); ``scoring`` (``softmax``, default, or ``sigmoid``: every expert's score is the
     logistic function of its own logit, the largest are chosen and are the weights);
     ``weight_input`` (the weight multiplies what the expert READS, ``sum_k expert_k(w_k x)``, instead of what
-    it puts out: the gated unit is not linear, so the two differ); optional tensor names below the prefix:
+    it puts out: the gated unit is not linear, so the two differ; the first product is, so the weight is
+    applied to both of its halves in the epilogue, ``act(w g) (w u)`` with ``g``, ``u`` the products of the
+    unweighted row); optional tensor names below the prefix:
     ``router`` (default ``gate.weight``), ``router_bias_name`` (default ``gate.bias``), ``expert`` (a format
     with ``{e}``, default ``experts.{e}.``), ``gate``, ``up``, ``down`` (default ``gate_proj.weight`` and so
     on; the shared expert's three matrices take the same names), ``shared`` (the shared expert's prefix,
@@ -314,7 +316,7 @@ class SparseMoE(FeedForward):
         shared = side = inv_perm = None
         overlap = self.sI > 0 and TUNING.shared_expert_overlap
         n = T * self.K
-        if self._by_pair(T) and not self.weight_input:
+        if self._by_pair(T):
             # decode-sized step: routing in one launch, no permutation; every used expert's weights
             # are read once and result rows are indexed by (token, slot) pair
             fork_first = T > TUNING.shared_expert_fork_after_routing_max_tokens
@@ -328,7 +330,9 @@ class SparseMoE(FeedForward):
                     want_probs=self.keep_routing, permute=False, bias=self.b_router, scoring=self.scoring)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
-            act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True, glu=self._glu())
+            # (weights on the experts' inputs: result rows are indexed by pair, as the weights are)
+            act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True, glu=self._glu(),
+                                              row_scale=w if self.weight_input else None)
             y = F.grouped_gemm_skinny_pairs(act, idx, self.w_down, False)
             if ctx.prefetch is not None:
                 # while the experts' rows are summed and normalised, the next layer's first weights arrive
@@ -350,23 +354,23 @@ class SparseMoE(FeedForward):
                 offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
-            src, gather = x, sorted_token
-            if self.weight_input:
-                # the experts read w * x: one weighted copy of the token's row per chosen expert, written straight
-                # into expert order (so nothing is left to gather), and the experts' rows are summed as they are
-                src, gather = F.scatter_rows_scaled(x, inv_perm, w), None
+            # The experts read w * x.  Their first product is linear in its input, W (w x) = w (W x), so the
+            # weight meets both halves of the gated unit in the product's epilogue, one number per row in
+            # expert order, and no weighted copy of the rows is made; the experts' rows are summed as they are.
+            scale = F.scatter_values(w, inv_perm) if self.weight_input else None
             if self._few_rows_per_expert(T):
                 # a few rows per expert: bound by reading each used expert once
-                act = F.grouped_gemm_skinny(src, gather, self.w_gate_up, offsets, n, True, glu=self._glu())
+                act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True, glu=self._glu(),
+                                            row_scale=scale)
                 y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)
             elif self._tc:
                 # many rows per expert: tensor-core tiles over the rows gathered into expert order
-                xs = src if gather is None else F.gather_rows(x, sorted_token)
-                act = F.grouped_gemm_tc(xs, self.w_gate_up, offsets, True, glu=self._glu())
+                xs = F.gather_rows(x, sorted_token)
+                act = F.grouped_gemm_tc(xs, self.w_gate_up, offsets, True, glu=self._glu(), row_scale=scale)
                 y = F.grouped_gemm_tc(act, self.w_down, offsets, False)
             else:
-                act = F.grouped_gemm_plain(src, gather, self.w_gate_up, offsets, n, True, self.rt.act,
-                                           glu=self._glu())
+                act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act,
+                                           glu=self._glu(), row_scale=scale)
                 y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
         if self.keep_routing:
             self.last_routing = (idx, w, probs)

@@ -3,6 +3,8 @@
 caches, with inputs made so that a fault shows: a key that stands out far back among hundreds, queries that match
 no key (whose weight the added key of the softmax must take), the first token of a sequence."""
 
+from types import SimpleNamespace
+
 import pytest
 import torch
 
@@ -181,6 +183,46 @@ def test_tensor_memory_attention_with_capped_scores_and_one_key_more(H, G, d, ca
         assert float((other - want).abs().max()) > 2e-2 * float(want.abs().max())      # the cap matters here
 
 
+@pytest.mark.parametrize("H,G,d,cap,split", [(4, 2, 64, 5.0, 128), (2, 2, 128, 30.0, 512), (6, 1, 128, 0.0, 256),
+                                             (3, 3, 64, 1.0, 512), (2, 1, 256, 8.0, 128)])
+def test_split_attention_of_single_tokens_with_capped_scores_and_one_key_more(H, G, d, cap, split):
+    """Two requests of unequal length decode side by side on the split-KV kernel: each against the plain
+    attention of its last token, with splits that end inside pages; a query that matches nothing gives its
+    weight to the added key."""
+    g = torch.Generator().manual_seed(H + d)
+    lens = [701, 130]
+    seqs = [[torch.randn(T, n, d, generator=g).to(torch.bfloat16).float() for n in (H, G, G)] for T in lens]
+    # the second request's last query stands against every one of its keys: scores as far below zero as the cap lets them
+    seqs[1][1][:, :, 0] = 3.0
+    seqs[1][0][-1] = 0.0
+    seqs[1][0][-1, :, 0] = -20.0
+    ps, pages = 16, 120
+    kc = torch.full((pages, G, ps, d), 99.0)
+    vc = torch.full((pages, G, ps, d), 99.0)
+    order = torch.randperm(pages, generator=g).tolist()
+    table = torch.full((2, 50), -1, dtype=torch.int32)
+    for b, (q, k, v) in enumerate(seqs):
+        for t in range(lens[b]):
+            if t % ps == 0:
+                table[b, t // ps] = order.pop()
+            kc[table[b, t // ps], :, t % ps], vc[table[b, t // ps], :, t % ps] = k[t], v[t]
+    qq = torch.stack([s[0][-1] for s in seqs]).to(torch.bfloat16).to(DEV)
+    splits = -(-max(lens) // split)
+    po, pml = torch.full((2 * H * splits * d,), 7.0, device=DEV), torch.full((2 * H * splits * 2,), 7.0, device=DEV)
+    for sink in (True, False):
+        got = F().decode_attention(qq, kc.to(torch.bfloat16).to(DEV), vc.to(torch.bfloat16).to(DEV), table.to(DEV),
+                                   i32([0, 1, 2]), i32(lens), po, pml, splits, 0, scale=0.15, split=split, softcap=cap,
+                                   sink=sink).float().cpu()
+        for b, (q, k, v) in enumerate(seqs):
+            want = plain_attention(q, k, v, 0.15, cap)[-1]
+            err = float((got[b].double() - want).abs().max()) / float(want.abs().max())
+            if sink:
+                assert err <= 1.2e-2, (b, err)
+            elif b == 1 and (cap == 0.0 or cap >= 5.0):
+                # (a cap of 1 holds every score above -1, and hundreds of such keys outweigh the added one)
+                assert err > 2e-2, err      # the query that matches nothing: without the added key it must attend
+
+
 @pytest.mark.parametrize("tensor_cores", [False, True, "memory"])
 @pytest.mark.parametrize("decoded", [False, True])
 @pytest.mark.parametrize("key", [0, 1, 63, 64, 65, 255, 256, 500, 699])
@@ -294,16 +336,56 @@ def test_sigmoid_router_in_both_routings(T, E, K):
         assert all(len(set(r)) == K for r in idx.cpu().tolist())
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_weighted_rows_in_expert_order(dtype):
-    T, K, W = 9, 3, 50
+def test_numbers_brought_into_expert_order():
     g = torch.Generator().manual_seed(3)
-    x, w = torch.randn(T, W, generator=g).to(dtype), torch.rand(T, K, generator=g)
-    dest = torch.randperm(T * K, generator=g).to(torch.int32)
-    got = F().scatter_rows_scaled(x.to(DEV), dest.to(DEV), w.to(DEV)).cpu()
-    for i in range(T * K):
-        want = (w.view(-1)[i] * x[i // K].float()).to(dtype)
-        assert torch.equal(got[int(dest[i])], want)
+    for n in (1, 27, 1000):
+        v = torch.rand(n, generator=g)
+        dest = torch.randperm(n, generator=g).to(torch.int32)
+        got = F().scatter_values(v.to(DEV), dest.to(DEV)).cpu()
+        want = torch.empty(n)
+        want[dest.long()] = v
+        assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("form", ["plain32", "plain16", "skinny", "pairs", "pairs_large", "tc"])
+def test_a_number_per_row_that_scales_both_halves_of_a_gated_unit(form):
+    """Every grouped product's epilogue: ``silu(s g) (s u)`` with ``g``, ``u`` the products of the unscaled row,
+    against the gated unit of the scaled row.  The scale matters: without it the result is far off."""
+    g = torch.Generator().manual_seed(len(form))
+    E, Kd, Nout = 5, 64, 96
+    w = (torch.randn(E, 2 * Nout, Kd, generator=g) * Kd ** -0.5).to(torch.bfloat16)
+    if form.startswith("pairs"):
+        T, K = (6, 2) if form == "pairs" else (50, 3)
+        x = torch.randn(T, Kd, generator=g).to(torch.bfloat16)
+        idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+        scale = 0.1 + torch.rand(T, K, generator=g)
+        rows, experts = x.repeat_interleave(K, dim=0), idx.reshape(-1).long()
+        call = lambda sc: F().grouped_gemm_skinny_pairs(x.to(DEV), idx.to(DEV), w.to(DEV), True, row_scale=sc)
+    else:
+        counts = [37, 0, 1, 150 if form == "tc" else 9, 16]
+        n = sum(counts)
+        offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+        rows = torch.randn(n, Kd, generator=g).to(torch.bfloat16)
+        experts = torch.repeat_interleave(torch.arange(E), torch.tensor(counts))
+        scale = 0.1 + torch.rand(n, generator=g)
+        dt = torch.float32 if form == "plain32" else torch.bfloat16
+        a, wd, off = rows.to(dt).to(DEV), w.to(dt).to(DEV), offsets.to(DEV)
+        if form.startswith("plain"):
+            call = lambda sc: F().grouped_gemm_plain(a, None, wd, off, n, True, dt, row_scale=sc)
+        elif form == "skinny":
+            call = lambda sc: F().grouped_gemm_skinny(a, None, wd, off, n, True, row_scale=sc)
+        else:
+            def call(sc):
+                out = F().grouped_gemm_tc(a, wd, off, True, row_scale=sc)
+                F().check_tc_status()
+                return out
+    xs = rows.double() * scale.reshape(-1, 1).double()
+    gu = torch.einsum("nk,nfk->nf", xs, w.double()[experts])
+    want = torch.nn.functional.silu(gu[:, :Nout]) * gu[:, Nout:]
+    got = call(scale.to(DEV)).double().cpu()
+    tol = 1e-5 if form == "plain32" else 1.2e-2
+    assert float((got - want).abs().max()) <= tol * float(want.abs().max())
+    assert float((call(None).double().cpu() - want).abs().max()) > 0.1 * float(want.abs().max())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -325,7 +407,7 @@ def test_expert_block_with_weights_on_the_inputs(dtype, T, W, E, K, ff, shared):
     part.load(t, rt)
     part.keep_routing = True
     x = torch.randn(T, W, generator=g).to(torch.bfloat16)
-    out = part.forward(x.to(rt.act).to(DEV), None)
+    out = part.forward(x.to(rt.act).to(DEV), SimpleNamespace(prefetch=None))      # (a step without weight prefetch)
     idx = part.last_routing[0].cpu().long()
     mlp = {"router": {"top": K}, "shared": {"ff": shared} if shared else None}
     rnd = pt.same if dtype == "float32" else pt.as_bfloat16
