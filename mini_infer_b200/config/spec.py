@@ -120,6 +120,8 @@ class ModelSpec:
     embedding_prefix: str = "model.embed_tokens."
     final_norm_prefix: str = "model.norm."
     lm_head_prefix: str = "lm_head."
+    # tensors a checkpoint of this model may carry that nothing reads (their presence is no error)
+    unused_tensors: Tuple[str, ...] = ()
 
     def validate(self) -> None:
         if not self.layers:

@@ -149,7 +149,7 @@ class Model:
     def load(self, source, rt: Runtime, strict: bool = True) -> None:
         from ..weights.loader import LazyTensors, check_manifest
         decls = self.tensor_decls()
-        allow = []
+        allow = list(self.spec.unused_tensors)
         tied = self.spec.lm_head.get("tied_to")
         if tied:
             # checkpoints of tied models often still carry the head; it is ignored, not an error

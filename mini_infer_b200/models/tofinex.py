@@ -67,8 +67,14 @@ def build_tofinex(config_json: Dict[str, Any]) -> ModelSpec:
     c = TofinexConfig.from_json_dict(config_json)
     shapes = config_json.get("tensor_shapes")
     W = c.width
-    layers = []
+    layers, unused = [], []
     for i, l in enumerate(c.layers):
+        # a writer that stores every layer alike leaves a blending weight in layers that blend nothing and a
+        # second norm in layers without a feed-forward
+        if not l.blends_values:
+            unused.append(f"l{i}.mix.vmix")
+        if l.mlp is None:
+            unused.append(f"l{i}.norm2")
         parts = {"mixer": LayerPart("mixer", _mixer_spec(c, i, shapes), "mix."),
                  "mixer_norm": LayerPart("norm", _norm(c, "norm1"), "")}
         if l.mlp is not None:
@@ -84,7 +90,7 @@ def build_tofinex(config_json: Dict[str, Any]) -> ModelSpec:
         final_norm=_norm(c, "final.norm"),
         lm_head=PartSpec("linear", {"vocab_size": c.vocab, "hidden_size": W, "tied_to": "embed",
                                     "softcap": c.logit_softcap}),
-        embedding_prefix="", final_norm_prefix="", lm_head_prefix="")
+        embedding_prefix="", final_norm_prefix="", lm_head_prefix="", unused_tensors=tuple(unused))
 
 
 register_architecture("Tofinex", build_tofinex,

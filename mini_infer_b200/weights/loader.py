@@ -73,7 +73,8 @@ def check_manifest(decls: Iterable[TensorDecl], source, allow_unexpected: Sequen
     for d in decls:
         if d.name in have:
             got = tuple(source.shape(d.name))
-            if got != tuple(d.shape):
+            # one number is one number, stored without a shape or as a vector of one
+            if (got or (1,)) != (tuple(d.shape) or (1,)):
                 wrong_shape.append((d.name, got, tuple(d.shape)))
             dt = source.dtype(d.name)
             if dt not in _FLOAT_DTYPES:

@@ -77,6 +77,42 @@ def test_a_checkpoint_without_the_first_blending_weight_is_described_too():
     assert decls == set(shapes)
 
 
+class _Header:
+    """Names, shapes and types as a checkpoint's header gives them."""
+
+    def __init__(self, weights):
+        self.w = weights
+
+    def names(self):
+        return list(self.w)
+
+    def shape(self, name):
+        return tuple(self.w[name].shape)
+
+    def dtype(self, name):
+        return self.w[name].dtype
+
+    def describe(self):
+        return "a header"
+
+
+def test_a_checkpoint_that_stores_every_layer_alike_fits():
+    """A blending weight in a layer that blends nothing, a second norm in a layer without a feed-forward and a
+    number stored as a vector of one are no errors; any other stray tensor is."""
+    from mini_infer_b200.weights.loader import WeightError, check_manifest
+    cfg = tt.CONFIG_A
+    w = tt.make_weights(cfg, 2)
+    w["l0.mix.vmix"] = torch.tensor(0.3, dtype=torch.bfloat16)                 # layer 0 blends nothing
+    w["l2.norm2"] = torch.ones(cfg["width"], dtype=torch.bfloat16)             # layer 2 has no feed-forward
+    w["l3.mix.vmix"] = w["l3.mix.vmix"].reshape(1)
+    spec = build_model_spec(dict(cfg, tensor_shapes={k: tuple(v.shape) for k, v in w.items()}))
+    model = Model(spec)
+    check_manifest(model.tensor_decls(), _Header(w), allow_unexpected=spec.unused_tensors)
+    w["l1.norm3"] = torch.ones(cfg["width"], dtype=torch.bfloat16)
+    with pytest.raises(WeightError):
+        check_manifest(model.tensor_decls(), _Header(w), allow_unexpected=spec.unused_tensors)
+
+
 def test_one_cache_group_per_geometry():
     assert len(Model(build_model_spec(tt.CONFIG_D)).kv_groups) == 2
     same = copy.deepcopy(tt.CONFIG_D)
