@@ -825,17 +825,22 @@ def _tofinex_kernel_work(cfg, T, B, ctx, decode):
         H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
         pairs = B * ctx if decode else T * (T + 1) // 2
         by = (B * ctx * G * (d + e) * 2 + B * H * (d + e) * 2) if decode else T * (H + G) * (d + e) * 2
-        for name in (("attn_mix_tc_kernel",) if decode else ("attn_mix_tc_kernel", "pt::attn_prefill_tc_kernel")):
+        for name in (("attn_mix_tc_kernel", "attn_decode_split_kernel") if decode
+                     else ("attn_mix_tc_kernel", "pt::attn_prefill_tc_kernel")):
             add(name, by, pairs * H * (2.0 * d + 2.0 * e))
         # float32 rows in (and the first layer's values once more), queries out, keys and values into the cache
-        add("rope_store_kernel", rows * ((H * d + G * (d + e)) * 6 + G * e * 4), 0)
+        for name in ("rope_store_kernel", "rope_store_vec_kernel"):
+            add(name, rows * ((H * d + G * (d + e)) * 6 + G * e * 4), 0)
         # a part's float32 output in, the residual read and written, its rounded copy written
         parts = 1 if L["mlp"] is None else 2
-        add("out_norm_add_kernel", parts * rows * W * (4 + 8 + 2), 0)
+        for name in ("out_norm_add_kernel", "out_norm_add_vec_kernel"):
+            add(name, parts * rows * W * (4 + 8 + 2), 0)
+            if L["mlp"] is not None and L["mlp"]["kind"] == "moe":
+                K = L["mlp"]["router"]["top"]
+                # the experts' rows and the shared expert's row (float32) join the out_norm_add above
+                add(name, rows * W * 4 * K, 0)
         if L["mlp"] is not None and L["mlp"]["kind"] == "moe":
             K = L["mlp"]["router"]["top"]
-            # the experts' rows and the shared expert's row (float32) join the out_norm_add above
-            add("out_norm_add_kernel", rows * W * 4 * K, 0)
             add("tc::gather_rows_kernel", rows * W * 2 * (1 + K), 0)
     add("softcap_rows_kernel", (B if decode else 1) * cfg["vocab"] * 8, 0)
     return out

@@ -97,6 +97,132 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
     }
 }
 
+// Head sizes and the rotated part multiples of four (of eight where halves are paired), rows on 16-byte
+// boundaries: a warp per query, key or value head, grid (tokens, ceil((nh + 2 nkv) / 8)).  A lane keeps its
+// groups of four of the head in registers from the sum of squares to the store (heads of up to 128 CH).  The
+// squares are added per lane in ascending order and then over the lanes: an order that depends on dk only.
+template <typename AT, int CH>
+__global__ void __launch_bounds__(256)
+rope_store_vec_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+                      const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping, AT* __restrict__ q_out,
+                      AT* __restrict__ k_cache, AT* __restrict__ v_cache, int nh, int nkv, int dk, int dv, int rot_dim,
+                      int page_size, const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                      int neighbours, const float* __restrict__ v_first, int64_t v_first_stride,
+                      const float* __restrict__ lam_ptr) {
+    extern __shared__ float trig[];                 // cos and sin of this token's rot_dim / 2 angles
+    wait_for_earlier_kernels();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int head = blockIdx.y * 8 + warp;
+    const int half = rot_dim / 2;
+    const int nqk = (nh + nkv) * dk;
+    const float* row = qkv + (int64_t)t * ((int64_t)nqk + (int64_t)nkv * dv);
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    if ((int)blockIdx.y * 8 < nh + nkv) {           // a block of value heads alone needs no angles
+        const float pos = (float)positions[t];
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float ang = pos * inv_freq[i];
+            trig[i] = cosf(ang);
+            trig[half + i] = sinf(ang);
+        }
+    }
+    __syncthreads();
+    if (head >= nh + 2 * nkv) return;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot - page * page_size;
+    if (head >= nh + nkv) {
+        if (slot < 0) return;
+        const int hk = head - nh - nkv;
+        const float4* src = reinterpret_cast<const float4*>(row + nqk + hk * dv);
+        const float4* fst = v_first ? reinterpret_cast<const float4*>(v_first + (int64_t)t * v_first_stride + hk * dv)
+                                    : nullptr;
+        const float lam = v_first ? lam_ptr[0] : 0.f;
+        AT* dst = v_cache + (((int64_t)page * nkv + hk) * page_size + off) * dv;
+        for (int c = lane; c < (dv >> 2); c += 32) {
+            float4 v = src[c];
+            if (fst) {
+                const float4 f = fst[c];
+                v.x = (1.0f - lam) * v.x + lam * f.x;
+                v.y = (1.0f - lam) * v.y + lam * f.y;
+                v.z = (1.0f - lam) * v.z + lam * f.z;
+                v.w = (1.0f - lam) * v.w + lam * f.w;
+            }
+            store4(dst + 4 * c, v);
+        }
+        return;
+    }
+    const bool is_q = head < nh;
+    if (!is_q && slot < 0) return;
+    const float4* hrow = reinterpret_cast<const float4*>(row + head * dk);
+    const int nc = dk >> 2;
+    float4 x[CH];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int c = lane + 32 * j;
+        x[j] = c < nc ? hrow[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += x[j].x * x[j].x;
+        ss += x[j].y * x[j].y;
+        ss += x[j].z * x[j].z;
+        ss += x[j].w * x[j].w;
+    }
+    const bool normed = q_gain != nullptr;
+    const float4* gain = reinterpret_cast<const float4*>(is_q ? q_gain : k_gain);
+    float r = 1.0f;
+    if (normed) {
+        ss = warp_sum(ss);
+        r = 1.0f / sqrtf(ss / (float)dk + eps);
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            const int c = lane + 32 * j;
+            if (c < nc) {
+                const float4 g = gain[c];
+                x[j].x = x[j].x * r * g.x;
+                x[j].y = x[j].y * r * g.y;
+                x[j].z = x[j].z * r * g.z;
+                x[j].w = x[j].w * r * g.w;
+            }
+        }
+    }
+    AT* dst = is_q ? q_out + (int64_t)t * nh * dk + head * dk
+                   : k_cache + (((int64_t)page * nkv + (head - nh)) * page_size + off) * dk;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int c = lane + 32 * j;
+        if (c >= nc) continue;
+        float4 v = x[j];
+        if (4 * c < rot_dim) {
+            if (neighbours) {
+                // (x, y) is pair 2c, (z, w) pair 2c + 1: the first becomes u cos - v sin, the second v cos + u sin
+                const float c0 = trig[2 * c], s0 = trig[half + 2 * c];
+                const float c1 = trig[2 * c + 1], s1 = trig[half + 2 * c + 1];
+                v.x = x[j].x * c0 - x[j].y * s0;
+                v.y = x[j].y * c0 + x[j].x * s0;
+                v.z = x[j].z * c1 - x[j].w * s1;
+                v.w = x[j].w * c1 + x[j].z * s1;
+            } else {
+                // dimension i < half is paired with i + half: the partner group lies with another lane
+                const bool first = 4 * c < half;
+                const int pc = first ? c + (half >> 2) : c - (half >> 2);
+                float4 o = hrow[pc];
+                if (normed) {
+                    const float4 g = gain[pc];
+                    o.x = o.x * r * g.x;
+                    o.y = o.y * r * g.y;
+                    o.z = o.z * r * g.z;
+                    o.w = o.w * r * g.w;
+                }
+                const int i = 4 * (first ? c : pc);
+                const float sg = first ? -1.0f : 1.0f;
+                v.x = x[j].x * trig[i] + sg * (o.x * trig[half + i]);
+                v.y = x[j].y * trig[i + 1] + sg * (o.y * trig[half + i + 1]);
+                v.z = x[j].z * trig[i + 2] + sg * (o.z * trig[half + i + 2]);
+                v.w = x[j].w * trig[i + 3] + sg * (o.w * trig[half + i + 3]);
+            }
+        }
+        store4(dst + 4 * c, v);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Block = 256 threads, QT consecutive queries of one request with all H heads: R = H * QT rows, row
 // r = h * QT + i.  Warp w owns the rows [w * rpw, (w + 1) * rpw) through softmax and P.V; lane l owns the
@@ -364,6 +490,25 @@ int mi_rope_store(const float* qkv, const int* positions, const float* inv_freq,
     if (v_first && (!lam || v_first_stride < (int64_t)nkv * dv)) {
         set_last_error("rope_store: blended values need their weight and rows of at least %d", nkv * dv);
         return kBadShape;
+    }
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                           reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                           reinterpret_cast<uintptr_t>(q_gain) | reinterpret_cast<uintptr_t>(k_gain) |
+                           reinterpret_cast<uintptr_t>(v_first);
+    if (dk % 4 == 0 && dv % 4 == 0 && rot_dim % (neighbours ? 4 : 8) == 0 && dk <= 512 && (ptrs & 15) == 0 &&
+        (!v_first || v_first_stride % 4 == 0)) {
+        const dim3 grid(T, (nh + 2 * nkv + 7) / 8);
+        const size_t smem = sizeof(float) * (rot_dim > 0 ? rot_dim : 1);
+#define MI_ROPE_STORE_VEC(CH)                                                                                        \
+    MI_DISPATCH_1(adtype, AT,                                                                                        \
+        launch_dependent(rope_store_vec_kernel<AT, CH>, grid, dim3(256), smem, stream, qkv, positions, inv_freq,     \
+                         slot_mapping, (AT*)q_out, (AT*)k_cache, (AT*)v_cache, nh, nkv, dk, dv, rot_dim, page_size,  \
+                         q_gain, k_gain, eps, neighbours, v_first, v_first_stride, lam))
+        if (dk <= 128) { MI_ROPE_STORE_VEC(1); }
+        else if (dk <= 256) { MI_ROPE_STORE_VEC(2); }
+        else { MI_ROPE_STORE_VEC(4); }
+#undef MI_ROPE_STORE_VEC
+        return finish_launch("rope_store");
     }
     MI_DISPATCH_1(adtype, AT,
         launch_dependent(rope_store_kernel<AT>, dim3(T), dim3(256),

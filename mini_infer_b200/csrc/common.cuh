@@ -70,6 +70,15 @@ __device__ __forceinline__ float glu_join_fast(float gate, float up, GluForm f) 
     return __fdividef(gate, 1.0f + __expf(-gate)) * up;
 }
 
+// four consecutive values of a row whose address is a multiple of four elements
+__device__ __forceinline__ void store4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float4& v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned int*>(&lo);
+    u.y = *reinterpret_cast<unsigned int*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

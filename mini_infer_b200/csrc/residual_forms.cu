@@ -187,6 +187,81 @@ out_norm_add_kernel(float* __restrict__ hidden, RowSum s, const WT* __restrict__
     }
 }
 
+// Rows of H = 4 n floats on 16-byte boundaries: a thread keeps VPT groups of four of the summed row in
+// registers between the sum of squares and the update (H <= 1024 VPT), 16 bytes a load.
+__device__ __forceinline__ void axpy4(float4& a, float w, const float4& x) {
+    a.x += w * x.x; a.y += w * x.y; a.z += w * x.z; a.w += w * x.w;
+}
+
+template <typename AT, typename WT, int VPT>
+__global__ void __launch_bounds__(256)
+out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restrict__ w, AT* __restrict__ x_out, int H,
+                        float eps, float mult) {
+    __shared__ float scratch[32];
+    wait_for_earlier_kernels();
+    const int64_t t = blockIdx.x;
+    const int nv = H >> 2;
+    float4 y[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) y[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (s.y) {
+        const float4* yv = reinterpret_cast<const float4*>(s.y + t * H);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = threadIdx.x + 256 * j;
+            if (i < nv) y[j] = yv[i];
+        }
+    } else {
+        for (int k = 0; k < s.K; ++k) {
+            const int64_t r = s.index ? s.index[t * s.K + k] : t * s.K + k;
+            const float wk = s.wk ? s.wk[t * s.K + k] : 1.0f;
+            const float4* rv = reinterpret_cast<const float4*>(s.rows + r * H);
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int i = threadIdx.x + 256 * j;
+                if (i < nv) axpy4(y[j], wk, rv[i]);
+            }
+        }
+        if (s.extra) {
+            const float g = s.scale[t];
+            const float4* ev = reinterpret_cast<const float4*>(s.extra + t * H);
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int i = threadIdx.x + 256 * j;
+                if (i < nv) axpy4(y[j], g, ev[i]);
+            }
+        }
+    }
+    // the residual row is on its way while the squares are added
+    float4* hv = reinterpret_cast<float4*>(hidden + t * H);
+    float4 h[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        h[j] = i < nv ? hv[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += y[j].x * y[j].x;
+        ss += y[j].y * y[j].y;
+        ss += y[j].z * y[j].z;
+        ss += y[j].w * y[j].w;
+    }
+    ss = block_sum(ss, scratch);
+    const float rr = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < nv) {
+            const int c = 4 * i;
+            h[j].x += mult * (y[j].x * rr * to_float(w[c]));
+            h[j].y += mult * (y[j].y * rr * to_float(w[c + 1]));
+            h[j].z += mult * (y[j].z * rr * to_float(w[c + 2]));
+            h[j].w += mult * (y[j].w * rr * to_float(w[c + 3]));
+            hv[i] = h[j];
+            if (x_out) store4(x_out + t * H + c, h[j]);
+        }
+    }
+}
+
 __global__ void softcap_rows_kernel(float* __restrict__ z, int64_t total, float cap) {
     wait_for_earlier_kernels();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -275,6 +350,21 @@ int mi_out_norm_add(float* hidden, const float* y, const float* rows, const int*
         return kBadShape;
     }
     const RowSum s{y, rows, index, wk, extra, scale, K};
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(y) |
+                           reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(extra) |
+                           reinterpret_cast<uintptr_t>(x_out);
+    if (H % 4 == 0 && H <= 8192 && (ptrs & 15) == 0) {
+#define MI_OUT_NORM_VEC(VPT)                                                                                         \
+    MI_DISPATCH_2(adtype, AT, wdtype, WT,                                                                            \
+        launch_dependent(out_norm_add_vec_kernel<AT, WT, VPT>, dim3(T), dim3(256), 0, stream, hidden, s,             \
+                         (const WT*)w, (AT*)x_out, H, eps, mult))
+        if (H <= 1024) { MI_OUT_NORM_VEC(1); }
+        else if (H <= 2048) { MI_OUT_NORM_VEC(2); }
+        else if (H <= 4096) { MI_OUT_NORM_VEC(4); }
+        else { MI_OUT_NORM_VEC(8); }
+#undef MI_OUT_NORM_VEC
+        return finish_launch("out_norm_add");
+    }
     const size_t smem = H <= 8192 ? sizeof(float) * H : 0;
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
         launch_dependent(out_norm_add_kernel<AT, WT>, dim3(T), dim3(256), smem, stream, hidden, s, (const WT*)w,

@@ -175,7 +175,8 @@ def test_a_far_kept_key_among_hundreds():
 # --------------------------------------------------------------------------- #
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,dk,dv,rot", [(4, 2, 16, 8, 8), (3, 3, 40, 40, 40), (1, 1, 6, 10, 0), (5, 1, 130, 64, 2)])
+@pytest.mark.parametrize("nh,nkv,dk,dv,rot", [(4, 2, 16, 8, 8), (3, 3, 40, 40, 40), (1, 1, 6, 10, 0), (5, 1, 130, 64, 2),
+                                              (2, 1, 256, 128, 128), (9, 3, 48, 16, 12), (2, 2, 384, 64, 384)])
 def test_head_norms_rotation_and_cache_write(dtype, nh, nkv, dk, dv, rot):
     T, ps, eps = 21, 4, 1e-5
     g = torch.Generator().manual_seed(nh + dk)

@@ -33,15 +33,20 @@ def runtime(dtype):
 # head norms, rotation of neighbouring dimensions, blended values, cache write
 # --------------------------------------------------------------------------- #
 
-@pytest.mark.parametrize("H,G,d,e,rot,blend", [(4, 2, 16, 10, 8, True), (5, 1, 12, 20, 12, False), (1, 1, 6, 3, 2, True),
-                                               (3, 3, 34, 34, 0, True), (8, 2, 96, 64, 96, True)])
+@pytest.mark.parametrize("H,G,d,e,rot,blend,pad", [
+    (4, 2, 16, 10, 8, True, 5), (5, 1, 12, 20, 12, False, 5), (1, 1, 6, 3, 2, True, 5), (3, 3, 34, 34, 0, True, 5),
+    (8, 2, 96, 64, 96, True, 5),
+    # sizes in fours and rows on 16-byte boundaries (a warp per head): all of a head rotated, part of it, none;
+    # heads of more than 128 and of more than 256 numbers; more heads than one block's eight warps
+    (8, 2, 96, 64, 96, True, 8), (4, 2, 160, 48, 80, True, 4), (2, 1, 320, 132, 320, False, 0),
+    (3, 1, 8, 4, 4, True, 12), (13, 13, 64, 64, 0, True, 8), (2, 2, 12, 12, 6, True, 4)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_norms_neighbour_rotation_and_blended_values_reach_the_cache(H, G, d, e, rot, blend, dtype):
+def test_norms_neighbour_rotation_and_blended_values_reach_the_cache(H, G, d, e, rot, blend, pad, dtype):
     T, first, ps = 21, 37, 8                  # the rows are positions 37 .. 57 of their request
     g = torch.Generator().manual_seed(H + d)
     qkv = torch.randn(T, (H + G) * d + G * e, generator=g)
     qg, kg = 1.0 + 0.3 * torch.randn(d, generator=g), 1.0 + 0.3 * torch.randn(d, generator=g)
-    wide = torch.randn(T, G * e + 5, generator=g)           # the first layer's values lie inside wider rows
+    wide = torch.randn(T, G * e + pad, generator=g)         # the first layer's values lie inside wider rows
     lam = torch.tensor([0.3])
     base, eps = 300.0, 1e-5
     pages = 10
@@ -52,7 +57,7 @@ def test_norms_neighbour_rotation_and_blended_values_reach_the_cache(H, G, d, e,
     if rot:
         inv = torch.pow(torch.tensor(base, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)
         inv = inv.float().to(DEV)
-    vf = wide.to(DEV)[:, 5:] if blend else None
+    vf = wide.to(DEV)[:, pad:] if blend else None
     q = F().rope_store(qkv.to(DEV), i32(list(range(first, first + T))), inv, rot, slots.to(DEV), kc, vc, H, G, d, e, ps,
                        dtype, qg.to(DEV), kg.to(DEV), eps, neighbours=True, v_first=vf,
                        blend=lam.to(DEV) if blend else None)
@@ -63,7 +68,7 @@ def test_norms_neighbour_rotation_and_blended_values_reach_the_cache(H, G, d, e,
         wq, wk = pt.rotate_neighbours(wq, rot, base, first), pt.rotate_neighbours(wk, rot, base, first)
     wv = x[:, (H + G) * d:].view(T, G, e)
     if blend:
-        wv = pt.blend_values(wv, wide[:, 5:].double(), float(lam))
+        wv = pt.blend_values(wv, wide[:, pad:].double(), float(lam))
     tol = 5e-6 if dtype == torch.float32 else 8e-3       # float32 angles at positions up to 57
     assert float((q.double().cpu() - wq).abs().max()) <= tol * float(wq.abs().max())
     for t in range(T):
@@ -269,7 +274,7 @@ def test_the_first_token_shares_its_weight_with_the_added_key():
 # a part's output normalised and added to the residual
 # --------------------------------------------------------------------------- #
 
-@pytest.mark.parametrize("T,W", [(1, 40), (7, 192), (33, 1000), (3, 9000)])
+@pytest.mark.parametrize("T,W", [(1, 40), (7, 192), (33, 1000), (3, 9000), (5, 1026), (4, 1536), (2, 4100), (2, 6000)])
 @pytest.mark.parametrize("dtype", [None, torch.bfloat16])
 def test_output_norm_and_scaled_addition(T, W, dtype):
     g = torch.Generator().manual_seed(T + W)
