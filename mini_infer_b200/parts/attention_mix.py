@@ -174,6 +174,8 @@ class HeadMixAttention(Mixer):
         q = F.rope_store(qkv, ctx.positions, self.inv_freq, self.rot_dim, view.slot_mapping, kc, vc, self.nh,
                          self.nkv, self.dk, self.dv, view.page_size, self.rt.act, self.q_gain, self.k_gain,
                          self.qk_eps, neighbours=self.neighbours, v_first=v_first, blend=self.blend_weight)
+        if ctx.prefetch is not None:
+            ctx.prefetch((self.w_o,))       # arrives while the attention over the cache runs
         if not self._tensor_cores:
             # float32: one kernel for every step, sums in an order that the cut of the step cannot change
             a = F.attention_mix(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,

@@ -263,6 +263,9 @@ class SparseMoE(FeedForward):
     def forward_deferred(self, x: torch.Tensor, ctx: StepContext) -> WeightedRowSum:
         """Everything but the weighted sum of the experts' rows (and of the shared expert's): the
         norm that follows forms it inside its own kernel."""
+        if ctx.prefetch is not None and self.sI > 0:
+            # the routing that comes first hardly touches memory: the shared expert's weights arrive beside it
+            ctx.prefetch((self.w_shared_gate_up, self.w_shared_down))
         return self._run(x, ctx, None)
 
     def forward_from_residual(self, hidden: torch.Tensor, delta, norm, ctx: StepContext):
