@@ -187,6 +187,7 @@ class ParallelResidual(Block):
         self.shared_norm = bool(self.params.get("shared_norm", False))
         self._side_stream = None
         self._ones = None
+        self._ones_before = []
         self.roles = {"mixer_norm": "norm", "mixer": "mixer"}
         if self.has_ff:
             self.roles.update({"feed_forward": "feed_forward"} if self.shared_norm else
@@ -236,6 +237,8 @@ class ParallelResidual(Block):
         if isinstance(f, WeightedRowSum) and f.extra is None:
             T = y.shape[0]
             if self._ones is None or self._ones.numel() < T or self._ones.device != y.device:
+                # a captured pass keeps reading the tensor it was captured with: a smaller one stays alive
+                self._ones_before.append(self._ones)
                 self._ones = torch.ones(max(T, 1024), dtype=torch.float32, device=y.device)
             return WeightedRowSum(f.rows, f.index, f.weights, y, self._ones[:T])
         return TensorSum(y, resolve(f))

@@ -159,6 +159,7 @@ class SparseMoE(FeedForward):
         self._shared_prefix = self.prefix + p.get("shared", "shared_expert.")
         self._shared_gate_name = self.prefix + p.get("shared_gate", "shared_expert_gate.weight")
         self._ones = None
+        self._ones_before = []
         self._router_name = self.prefix + p.get("router", "gate.weight")
         self._router_bias_name = self.prefix + p.get("router_bias_name", "gate.bias")
         self._expert_format = p.get("expert", "experts.{e}.")
@@ -263,7 +264,7 @@ class SparseMoE(FeedForward):
     def forward_deferred(self, x: torch.Tensor, ctx: StepContext) -> WeightedRowSum:
         """Everything but the weighted sum of the experts' rows (and of the shared expert's): the
         norm that follows forms it inside its own kernel."""
-        if ctx.prefetch is not None and self.sI > 0:
+        if ctx is not None and ctx.prefetch is not None and self.sI > 0:
             # the routing that comes first hardly touches memory: the shared expert's weights arrive beside it
             ctx.prefetch((self.w_shared_gate_up, self.w_shared_down))
         return self._run(x, ctx, None)
@@ -289,6 +290,8 @@ class SparseMoE(FeedForward):
     def _unit_weights(self, T: int, device) -> torch.Tensor:
         """``[T, K]`` ones: the weights of a sum whose rows were weighted on their way in."""
         if self._ones is None or self._ones.shape[0] < T or self._ones.device != device:
+            # a captured pass keeps reading the tensor it was captured with: a smaller one stays alive
+            self._ones_before.append(self._ones)
             self._ones = torch.ones(max(T, 256), self.K, dtype=torch.float32, device=device)
         return self._ones[:T]
 

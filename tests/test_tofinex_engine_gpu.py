@@ -142,6 +142,21 @@ def test_long_decoding_with_slots_and_pages_used_again(models, dtype):
     assert runner.cache.used_pages() == [0] * len(runner.cache.pools)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_longer_prompts_after_a_captured_decode_pass(models, dtype):
+    """A request of one token captures the decode pass; then prompts arrive that are each longer than any step
+    before, and every one's last tokens replay that pass: what a part keeps from step to step (a vector of
+    ones, say) must not move under a captured pass when a longer step makes it grow."""
+    folder, cfg, w = models["A" if dtype == "float32" else "C"]
+    runner = runner_for(folder, dtype, page_size=16, num_pages=60, max_requests=4, max_tokens_per_step=700,
+                        max_context=700)
+    reqs = tt.random_requests(cfg, [1, 40, 300, 38, 650, 36], seed=12)
+    for rid, toks in reqs.items():
+        steps = traces.tail_decoded({rid: toks}, tail=6) if len(toks) > 6 else traces.whole({rid: toks})
+        run_and_check(runner, steps, cfg, w, {rid: toks}, dtype)
+    assert runner.graph_replays >= 30
+
+
 def test_a_slot_and_its_pages_serve_one_request_after_another(models):
     folder, cfg, w = models["B"]
     runner = runner_for(folder, "float32", max_requests=1, num_pages=12)
