@@ -21,6 +21,9 @@
 //
 // `sink`: the softmax counts one key more, of score 0 and without a value: p_j = exp(s_j) / (1 + sum exp(s_j)).
 // The running maximum then starts at 0 and the running sum at 1 instead of at -inf and 0.
+//
+// `head_bias` (a number per head): no softmax.  The weight of a visible key is logistic(score + head_bias[h]) by
+// itself, and a query's weights are not normalised over its keys: out = sum_j logistic(s_j + b_h) v_j.
 
 #include "common.cuh"
 
@@ -240,7 +243,7 @@ attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const 
                 const float* __restrict__ mix, const int* __restrict__ block_table, const int* __restrict__ q_start,
                 const int* __restrict__ kv_len, AT* __restrict__ out, int H, int G, int dk, int dv, int page_size,
                 int max_pages, int window, float scale, float cap, int QT, int KT, int rpw, int keep_first, int vrs,
-                int sink) {
+                int sink, const float* __restrict__ head_bias) {
     constexpr int RPW = MixCfg<AT, CPL>::RPW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     wait_for_earlier_kernels();
@@ -369,6 +372,13 @@ attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const 
             const int r = warp * rpw + m;
             if (m < rpw && r < R) {
                 float* prow = S2 + r * SP;
+                if (head_bias) {
+                    // every key weighs in by itself: nothing to rescale, nothing to sum
+                    const float hb = head_bias[r / QT];
+                    for (int j = lane; j < KT; j += 32)
+                        prow[j] = prow[j] == -INFINITY ? 0.f : 1.0f / (1.0f + expf(-(prow[j] + hb)));
+                    continue;
+                }
                 float tmax = -INFINITY;
                 for (int j = lane; j < KT; j += 32) tmax = fmaxf(tmax, prow[j]);
                 tmax = warp_max(tmax);
@@ -420,7 +430,7 @@ attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const 
         if (m < rpw && r < R) {
             const int h = r / QT, i = r - h * QT;
             if (i < nq) {
-                const float inv = l_run[m] > 0.f ? 1.f / l_run[m] : 0.f;
+                const float inv = head_bias ? 1.f : (l_run[m] > 0.f ? 1.f / l_run[m] : 0.f);
                 AT* o = out + ((int64_t)(q0 + qt * QT + i) * H + h) * dv;
 #pragma unroll
                 for (int n = 0; n < CPL; ++n) {
@@ -524,11 +534,17 @@ int mi_attn_mix_supported(int H, int G, int dk, int dv, int esize) {
     return plan_attn_mix(H, G, dk, dv, esize, false).ok && plan_attn_mix(H, G, dk, dv, esize, true).ok;
 }
 
-int mi_attn_mix(const void* q, const void* k_cache, const void* v_cache, int adtype, const float* mix,
-                const int* block_table, const int* q_start, const int* kv_len, void* out, int B, int max_q_len,
-                int H, int G, int dk, int dv, int page_size, int max_pages, int window, float scale, float cap,
-                int keep_first, int vrs, int sink, cudaStream_t stream) {
+// head_bias: null, or a number per head that makes every visible key's weight logistic(score + head_bias[h])
+// instead of its share of a softmax (then without `sink`)
+int mi_attn_mix_form(const void* q, const void* k_cache, const void* v_cache, int adtype, const float* mix,
+                     const int* block_table, const int* q_start, const int* kv_len, void* out, int B, int max_q_len,
+                     int H, int G, int dk, int dv, int page_size, int max_pages, int window, float scale, float cap,
+                     int keep_first, int vrs, int sink, const float* head_bias, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return kOk;
+    if (head_bias && sink) {
+        set_last_error("mixed-head attention: a key more belongs to a softmax, not to weights that are not normalised");
+        return kBadShape;
+    }
     if (keep_first < 0 || vrs < dv) {
         set_last_error("mixed-head attention: %d kept first keys, value rows of %d every %d elements", keep_first, dv, vrs);
         return kBadShape;
@@ -553,7 +569,7 @@ int mi_attn_mix(const void* q, const void* k_cache, const void* v_cache, int adt
         launch_dependent(attn_mix_kernel<AT, CPL>, grid, dim3(256), p.smem, stream, (const AT*)q,            \
                          (const AT*)k_cache, (const AT*)v_cache, mix, block_table, q_start, kv_len, (AT*)out, \
                          H, G, dk, dv, page_size, max_pages, window, scale, cap, p.QT, p.KT, p.rpw,          \
-                         keep_first, vrs, sink);                                                              \
+                         keep_first, vrs, sink, head_bias);                                                   \
     })
     if (cpl <= 1) MI_MIX_LAUNCH(1);
     else if (cpl <= 2) MI_MIX_LAUNCH(2);
@@ -561,6 +577,14 @@ int mi_attn_mix(const void* q, const void* k_cache, const void* v_cache, int adt
     else MI_MIX_LAUNCH(8);
 #undef MI_MIX_LAUNCH
     return finish_launch("attn_mix");
+}
+
+int mi_attn_mix(const void* q, const void* k_cache, const void* v_cache, int adtype, const float* mix,
+                const int* block_table, const int* q_start, const int* kv_len, void* out, int B, int max_q_len,
+                int H, int G, int dk, int dv, int page_size, int max_pages, int window, float scale, float cap,
+                int keep_first, int vrs, int sink, cudaStream_t stream) {
+    return mi_attn_mix_form(q, k_cache, v_cache, adtype, mix, block_table, q_start, kv_len, out, B, max_q_len, H, G, dk,
+                            dv, page_size, max_pages, window, scale, cap, keep_first, vrs, sink, nullptr, stream);
 }
 
 }  // extern "C"

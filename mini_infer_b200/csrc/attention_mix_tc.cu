@@ -16,6 +16,9 @@
 // and unnormalised output; a merge kernel finishes), since one block per request cannot pull a window of
 // keys from memory fast enough.
 //
+// With `head_bias` (a number per head) there is no softmax: a visible key's weight is logistic(score + head_bias[h]),
+// not normalised over the keys, so nothing is rescaled and the partial results of a split step are simply added.
+//
 // Built for value sizes 64 and 128 and key sizes that are multiples of 16.  The accumulators of 16 heads of
 // value size 128 (32 of 64) fill one block's registers; with more heads several blocks share a query tile,
 // each forming all heads' scores and finishing its own group of heads.  Shapes whose tiles do not fit shared
@@ -57,7 +60,8 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ block_table, const int* __restrict__ q_start,
                    const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int H, int G, int dk, int page_size, int max_pages, int window,
-                   float scale, float cap, int splits, int hgroups, int keep_first, int vrs, int sink) {
+                   float scale, float cap, int splits, int hgroups, int keep_first, int vrs, int sink,
+                   const float* __restrict__ head_bias) {
     constexpr int DV = NT * 8;
     constexpr int SP = KT + 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -280,6 +284,15 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                     mx0 = fmaxf(mx0, fmaxf(p[nt][0], p[nt][1]));
                     mx1 = fmaxf(mx1, fmaxf(p[nt][2], p[nt][3]));
                 }
+                if (head_bias) {
+                    // every key weighs in by itself (a masked score of -inf gives 0): nothing to rescale
+                    const float hb = head_bias[h];
+#pragma unroll
+                    for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            p[nt][x] = p[nt][x] == -INFINITY ? 0.f : __fdividef(1.0f, 1.0f + __expf(-(p[nt][x] + hb)));
+                } else {
                 mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
                 mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
                 mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
@@ -305,6 +318,7 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                 for (int nt = 0; nt < NT; ++nt) {
                     acc[hh][nt][0] *= al0; acc[hh][nt][1] *= al0;
                     acc[hh][nt][2] *= al1; acc[hh][nt][3] *= al1;
+                }
                 }
                 const __nv_bfloat16* vb = Vb + (size_t)g * KT * dvp;
 #pragma unroll
@@ -345,7 +359,8 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                     if ((lane & 3) == 0) { part_ml[base * 2] = m_run[hh][0]; part_ml[base * 2 + 1] = l0; }
                 }
             } else {
-                const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+                const float i0 = head_bias ? 1.f : (l0 > 0.f ? 1.f / l0 : 0.f);
+                const float i1 = head_bias ? 1.f : (l1 > 0.f ? 1.f / l1 : 0.f);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     if (r0 < nq)
@@ -366,12 +381,22 @@ constexpr int kMergeMaxSplits = 12288;          // two floats a split in shared 
 __global__ void __launch_bounds__(128)
 attn_mix_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                       const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, int H, int DV, int splits,
-                      int sink) {
+                      int sink, int plain_sum) {
     extern __shared__ float merge_sh[];         // [splits] weights, [splits] sums
     float* wgt = merge_sh;
     float* lsum = merge_sh + splits;
     wait_for_earlier_kernels();
     const int b = blockIdx.y, h = blockIdx.x;
+    if (plain_sum) {
+        // weights that are not normalised: the splits' partial outputs are added as they are, in split order
+        const int row0 = q_start[b];
+        for (int c = threadIdx.x; c < DV; c += blockDim.x) {
+            float o = 0.f;
+            for (int s = 0; s < splits; ++s) o += part_o[(((size_t)b * splits + s) * H + h) * DV + c];
+            out[((size_t)row0 * H + h) * DV + c] = __float2bfloat16_rn(o);
+        }
+        return;
+    }
     for (int s = threadIdx.x; s < splits; s += blockDim.x) {
         const float2 ml = *reinterpret_cast<const float2*>(part_ml + (((size_t)b * splits + s) * H + h) * 2);
         wgt[s] = ml.x;
@@ -431,11 +456,16 @@ int mi_attn_mix_tc_supported(int H, int G, int dk, int dv) { return tc_plan(H, G
 // splits a step of single tokens is cut into, given the longest span of keys a query can see
 int mi_attn_mix_tc_splits(int span) { return (span + kTcSplitKeys - 1) / kTcSplitKeys + 1; }
 
-int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, const float* mix, const int* block_table,
-                   const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
-                   int max_q_len, int H, int G, int dk, int dv, int page_size, int max_pages, int window,
-                   float scale, float cap, int splits, int keep_first, int vrs, int sink, cudaStream_t stream) {
+int mi_attn_mix_tc_form(const void* q, const void* k_cache, const void* v_cache, const float* mix,
+                        const int* block_table, const int* q_start, const int* kv_len, void* out, float* part_o,
+                        float* part_ml, int B, int max_q_len, int H, int G, int dk, int dv, int page_size,
+                        int max_pages, int window, float scale, float cap, int splits, int keep_first, int vrs,
+                        int sink, const float* head_bias, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return kOk;
+    if (head_bias && sink) {
+        set_last_error("mixed-head attention (tensor cores): a key more belongs to a softmax, not to weights that are not normalised");
+        return kBadShape;
+    }
     if (keep_first < 0 || vrs < dv || vrs % 8) {
         set_last_error("mixed-head attention (tensor cores): %d kept first keys, value rows of %d every %d elements",
                        keep_first, dv, vrs);
@@ -460,7 +490,7 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
         launch_dependent(attn_mix_tc_kernel<HPW, NT, KT>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)q, \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, mix, block_table, q_start, \
                          kv_len, (__nv_bfloat16*)out, part_o, part_ml, H, G, dk, page_size, max_pages, window,  \
-                         scale, cap, splits, hgroups, keep_first, vrs, sink);                                   \
+                         scale, cap, splits, hgroups, keep_first, vrs, sink, head_bias);                        \
     } while (0)
 #define MI_TC_KT(HPW, NT) do { if (kt == 32) MI_TC_LAUNCH(HPW, NT, 32); else MI_TC_LAUNCH(HPW, NT, 16); } while (0)
     if (dv == 128) {
@@ -476,10 +506,20 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
         if (merge_smem > 48 * 1024)
             cudaFuncSetAttribute(attn_mix_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem);
         launch_dependent(attn_mix_merge_kernel, dim3(H, B), dim3(128), merge_smem, stream, (const float*)part_o,
-                         (const float*)part_ml, q_start, (__nv_bfloat16*)out, H, dv, splits, sink);
+                         (const float*)part_ml, q_start, (__nv_bfloat16*)out, H, dv, splits, sink,
+                         head_bias ? 1 : 0);
         launched = 2;
     }
     return finish_launch("attn_mix_tc", launched);
+}
+
+int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, const float* mix, const int* block_table,
+                   const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
+                   int max_q_len, int H, int G, int dk, int dv, int page_size, int max_pages, int window,
+                   float scale, float cap, int splits, int keep_first, int vrs, int sink, cudaStream_t stream) {
+    return mi_attn_mix_tc_form(q, k_cache, v_cache, mix, block_table, q_start, kv_len, out, part_o, part_ml, B,
+                               max_q_len, H, G, dk, dv, page_size, max_pages, window, scale, cap, splits, keep_first,
+                               vrs, sink, nullptr, stream);
 }
 
 }  // extern "C"

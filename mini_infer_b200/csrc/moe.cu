@@ -284,6 +284,9 @@ moe_router_logits_small_kernel(const AT* __restrict__ x, const WT* __restrict__ 
 // `norm_topk` of the selection carries two switches: bit 0, the chosen weights are divided by their sum; bit 1
 // (kScoreSigmoid), the experts are scored one by one with the logistic function instead of by a softmax.
 constexpr int kScoreSigmoid = 2;
+// Bits 8..19 and 20..31 of the same word: the number of equal groups of neighbouring experts and how many of them
+// stay eligible (softmax scoring; 0 or 1 groups, or all kept: every expert is eligible).
+constexpr int kGroupCountShift = 8, kGroupKeepShift = 20;
 
 // Softmax over all experts, K rounds of arg-max (lowest index among equals), weights; one warp per
 // token.  `p` is the warp's E floats of shared memory and holds the token's logits, `mx` the largest
@@ -343,6 +346,34 @@ __device__ __forceinline__ void router_select_loaded(float mx, float gate_logit,
         if (probs_out) probs_out[(int64_t)t * E + e] = v;
     }
     __syncwarp();
+    // Experts in equal groups of neighbours, of which only the best few stay eligible (a group's score is its
+    // largest score).  The kept groups are marked by the sign of their scores, which is exact and undone below;
+    // the others' scores become -inf, so the rounds that follow never choose them.
+    const int n_groups = (norm_topk >> kGroupCountShift) & 0xfff, n_keep = (norm_topk >> kGroupKeepShift) & 0xfff;
+    if (n_groups > 1 && n_keep < n_groups) {
+        const int gs = E / n_groups;
+        for (int r = 0; r < n_keep; ++r) {
+            float best = -INFINITY;
+            int bg = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                if (signbit(p[g * gs])) continue;               // kept already
+                float gm = p[g * gs];
+                for (int e = 1; e < gs; ++e) gm = fmaxf(gm, p[g * gs + e]);
+                if (gm > best) { best = gm; bg = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+                if (ov > best || (ov == best && og < bg)) { best = ov; bg = og; }
+            }
+            if (bg != 0x7fffffff)
+                for (int e = lane; e < gs; e += 32) p[bg * gs + e] = -p[bg * gs + e];
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) p[e] = signbit(p[e]) ? -p[e] : -INFINITY;
+        __syncwarp();
+    }
     float wsum = 0.f;
     float my_w = 0.f;  // lane k keeps weight k (K <= 32 checked on the host)
     for (int k = 0; k < K; ++k) {

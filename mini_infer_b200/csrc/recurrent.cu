@@ -1,9 +1,12 @@
 // Mixers that carry a fixed-size state per request instead of a cache that grows:
 //
 //   causal_conv_silu   short causal convolution over time per channel (+ bias) and silu, with the last
-//                      taps-1 inputs of a request kept in its state slot between steps
-//   delta_scan         gated delta rule with one decay per head and key channel:
+//                      taps-1 inputs of a request kept in its state slot between steps; the residual form
+//                      (causal_conv_residual) puts out x_t + conv(x)_t instead, without an activation
+//   delta_scan         gated delta rule with one decay per head and key channel (or one per head):
 //                        S <- diag(g_t) S ;  u = beta_t (v_t - S^T k_t) ;  S <- S + k_t u^T ;  o_t = S^T q_t
+//                      and, without the correction, gated linear attention:
+//                        S <- diag(g_t) S + k_t v_t^T ;  o_t = S^T q_t
 //   ssd_scan           selective state-space recurrence with a scalar decay per head (Mamba-2):
 //                        S <- exp(-A dt_t) S + dt_t B_t x_t^T ;  y_t = S^T C_t + D x_t
 //   gated_group_rmsnorm  RMS norm over equal groups of a row, with a gate before (silu) or after (sigmoid) it
@@ -35,12 +38,13 @@ constexpr int kMaxTaps = 8;
 // come from the request's state (time-major: state[j * C + c] is the input at local position
 // j - (taps-1)), zeros for a fresh request because a new slot is zeroed.
 // ---------------------------------------------------------------------------
-template <typename WT>
+// RES: out = x_t + conv(x)_t, in the type OT, instead of silu(conv(x)_t).
+template <typename WT, typename OT, bool RES>
 __global__ void __launch_bounds__(256)
 causal_conv_silu_kernel(const float* __restrict__ x, int ldx, const WT* __restrict__ w, const WT* __restrict__ bias,
                         const float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
                         const int* __restrict__ req_of_token, const int* __restrict__ state_slot,
-                        float* __restrict__ out, int ld_out, int C, int taps, int T) {
+                        OT* __restrict__ out, int ld_out, int C, int taps, int T) {
     wait_for_earlier_kernels();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
@@ -62,18 +66,18 @@ causal_conv_silu_kernel(const float* __restrict__ x, int ldx, const WT* __restri
                 acc += wt[j] * v;
             }
         }
-        out[(int64_t)t * ld_out + c] = silu_f(acc);
+        out[(int64_t)t * ld_out + c] = from_float<OT>(RES ? x[(int64_t)t * ldx + c] + acc : silu_f(acc));
     }
 }
 
 // The same for four neighbouring channels per thread, sixteen bytes per access: rows, state and output whose
 // channel offsets and strides are multiples of four floats.
-template <typename WT>
+template <typename WT, typename OT, bool RES>
 __global__ void __launch_bounds__(128)
 causal_conv_silu_vec4_kernel(const float* __restrict__ x, int ldx, const WT* __restrict__ w, const WT* __restrict__ bias,
                              const float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
                              const int* __restrict__ req_of_token, const int* __restrict__ state_slot,
-                             float* __restrict__ out, int ld_out, int C, int taps, int T) {
+                             OT* __restrict__ out, int ld_out, int C, int taps, int T) {
     wait_for_earlier_kernels();
     const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
     if (c >= C) return;
@@ -99,8 +103,12 @@ causal_conv_silu_vec4_kernel(const float* __restrict__ x, int ldx, const WT* __r
                 acc.x += wt[0][j] * v.x; acc.y += wt[1][j] * v.y; acc.z += wt[2][j] * v.z; acc.w += wt[3][j] * v.w;
             }
         }
-        *reinterpret_cast<float4*>(out + (int64_t)t * ld_out + c) =
-            make_float4(silu_f(acc.x), silu_f(acc.y), silu_f(acc.z), silu_f(acc.w));
+        if (RES) {
+            const float4 xt = *reinterpret_cast<const float4*>(x + (int64_t)t * ldx + c);
+            store4(out + (int64_t)t * ld_out + c, make_float4(xt.x + acc.x, xt.y + acc.y, xt.z + acc.z, xt.w + acc.w));
+        } else {
+            store4(out + (int64_t)t * ld_out + c, make_float4(silu_f(acc.x), silu_f(acc.y), silu_f(acc.z), silu_f(acc.w)));
+        }
     }
 }
 
@@ -172,43 +180,58 @@ __device__ __forceinline__ float shared_f1(uint32_t a) {
 __device__ __forceinline__ int scan_row(int r, int m, int x) { return 4 * (r + kScanLanes * m) + x; }
 
 // What the delta rule reads per (token, head), made ready by a kernel of its own (all tokens at once, instead
-// of once per slice of value columns inside the walk): prep[t][h] = [unit q * q_scale | unit k | decay | beta, 0, 0, 0],
-// the three vectors padded to DP rows with 0, 0 and 1.  qkv: [T, ld_qkv] float, q heads at column 0 (G x d),
-// k heads at G*d; beta_raw: [T, ld_beta] (H columns); a_raw: [T, ld_a] (H x d columns, before dt_bias and
-// softplus).
+// of once per slice of value columns inside the walk): prep[t][h] = [q | k | decay | beta, 0, 0, 0], the three
+// vectors padded to DP rows with 0, 0 and 1.  qkv: [T, ld_qkv] float, q heads at column 0 (G x d), k heads at
+// G*d; beta_raw: [T, ld_beta] (H columns); a_raw: [T, ld_a].  `form` says what the vectors are:
+//   0  unit q (times q_scale), unit k; a decay per head and key channel, exp(-exp(a_log[h]) softplus(a + dt_bias))
+//      with a and dt_bias laid out H x d
+//   1  the same with ONE decay per head: a and dt_bias have H columns
+//   2  q times q_scale and k as they are; a decay per key channel, sigmoid(a + dt_bias)^(1 / tau), laid out
+//      H x d (a_log and beta_raw are not read; the write strength is 1)
+enum DeltaForm : int { kDecayPerChannel = 0, kDecayPerHead = 1, kSigmoidDecay = 2 };
+
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __restrict__ beta_raw, int ld_beta,
                      const float* __restrict__ a_raw, int ld_a, const float* __restrict__ a_log,
                      const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int G, int d, int DP,
-                     float q_scale) {
+                     float q_scale, int form, float tau) {
     __shared__ float scratch[32];
     wait_for_earlier_kernels();
     const int64_t t = blockIdx.x;
     const int h = blockIdx.y, hk = h / (H / G);
     const float* qrow = qkv + t * ld_qkv + (int64_t)hk * d;
     const float* krow = qkv + t * ld_qkv + (int64_t)(G + hk) * d;
+    float qn = q_scale, kn = 1.0f;
+    if (form != kSigmoidDecay) {
+        float qq = 0.f, kk = 0.f;
+        for (int i = threadIdx.x; i < d; i += 128) { const float a = qrow[i], c = krow[i]; qq += a * a; kk += c * c; }
+        qq = block_sum(qq, scratch);
+        kk = block_sum(kk, scratch);
+        qn = q_scale / sqrtf(qq + 1e-6f);
+        kn = 1.0f / sqrtf(kk + 1e-6f);
+    }
+    const float neg_a = form == kSigmoidDecay ? 0.f : -expf(a_log[h]);
+    const float head_decay = form == kDecayPerHead ? expf(neg_a * softplus_f(a_raw[t * ld_a + h] + dt_bias[h])) : 1.f;
     const float* arow = a_raw + t * ld_a + (int64_t)h * d;
-    float qq = 0.f, kk = 0.f;
-    for (int i = threadIdx.x; i < d; i += 128) { const float a = qrow[i], c = krow[i]; qq += a * a; kk += c * c; }
-    qq = block_sum(qq, scratch);
-    kk = block_sum(kk, scratch);
-    const float qn = q_scale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
-    const float neg_a = -expf(a_log[h]);
     float* row = prep + (t * H + h) * (3 * DP + 4);
     for (int i = threadIdx.x; i < DP; i += 128) {
         float qv = 0.f, kv = 0.f, gv = 1.f;
         if (i < d) {
             qv = qrow[i] * qn;
             kv = krow[i] * kn;
-            gv = expf(neg_a * softplus_f(arow[i] + dt_bias[(int64_t)h * d + i]));
+            if (form == kDecayPerChannel) gv = expf(neg_a * softplus_f(arow[i] + dt_bias[(int64_t)h * d + i]));
+            else if (form == kDecayPerHead) gv = head_decay;
+            else gv = expf(-softplus_f(-(arow[i] + dt_bias[(int64_t)h * d + i])) / tau);   // log sigmoid(z) = -softplus(-z)
         }
         row[i] = qv; row[DP + i] = kv; row[2 * DP + i] = gv;
     }
-    if (threadIdx.x < 4) row[3 * DP + threadIdx.x] = threadIdx.x == 0 ? sigmoid_f(beta_raw[t * ld_beta + h]) : 0.f;
+    if (threadIdx.x < 4)
+        row[3 * DP + threadIdx.x] = threadIdx.x == 0 ? (form == kSigmoidDecay ? 1.f : sigmoid_f(beta_raw[t * ld_beta + h])) : 0.f;
 }
 
 // The walk.  prep as delta_prepare_kernel leaves it; v heads at column v_col0 of qkv (H x dv).  out: [T, H*dv].
-template <int RP>
+// Without DELTA the write is the value itself, u = v_t (gated linear attention): S^T k_t is never formed.
+template <int RP, bool DELTA>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, const float* __restrict__ prep,
                   float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
@@ -280,11 +303,15 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, con
                         const float4 g4 = shared_f4(qa + (2 * DP + 4 * kScanLanes * m) * 4);
                         k4[m] = shared_f4(qa + (DP + 4 * kScanLanes * m) * 4);
                         s[4 * m] *= g4.x; s[4 * m + 1] *= g4.y; s[4 * m + 2] *= g4.z; s[4 * m + 3] *= g4.w;
-                        a0 += s[4 * m] * k4[m].x; a1 += s[4 * m + 1] * k4[m].y; a2 += s[4 * m + 2] * k4[m].z; a3 += s[4 * m + 3] * k4[m].w;
+                        if (DELTA) {
+                            a0 += s[4 * m] * k4[m].x; a1 += s[4 * m + 1] * k4[m].y; a2 += s[4 * m + 2] * k4[m].z; a3 += s[4 * m + 3] * k4[m].w;
+                        }
                     }
-                    const float acc = lanes_sum((a0 + a1) + (a2 + a3));
-                    const float u = shared_f1(rows_a + (uint32_t)(tt * ROW + 3 * DP) * 4u) *
-                                    (shared_f1(vs_a + (uint32_t)(tt * kScanCols + lc) * 4u) - acc);
+                    float u = shared_f1(vs_a + (uint32_t)(tt * kScanCols + lc) * 4u);
+                    if (DELTA) {
+                        const float acc = lanes_sum((a0 + a1) + (a2 + a3));
+                        u = shared_f1(rows_a + (uint32_t)(tt * ROW + 3 * DP) * 4u) * (u - acc);
+                    }
                     float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
                     for (int m = 0; m < MV; ++m) {
@@ -462,6 +489,7 @@ ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
 // One block per (token, group of `gs` columns):
 //   mode 0:  z = y * silu(gate);  out = z * rsqrt(mean(z^2) + eps) * w        (gate before the norm)
 //   mode 1:  out = y * rsqrt(mean(y^2) + eps) * w * sigmoid(gate)             (gate after the norm)
+//   mode 2:  out = y * rsqrt(mean(y^2) + eps) * w * silu(gate)
 // w has `wlen` entries and column c of the row uses w[c % wlen].
 // ---------------------------------------------------------------------------
 template <typename AT, typename WT>
@@ -505,6 +533,7 @@ gated_group_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict_
             v.x *= rr * to_float(w[wi]); v.y *= rr * to_float(w[wi + 1]);
             v.z *= rr * to_float(w[wi + 2]); v.w *= rr * to_float(w[wi + 3]);
             if (mode == 1) { v.x *= sigmoid_f(g.x); v.y *= sigmoid_f(g.y); v.z *= sigmoid_f(g.z); v.w *= sigmoid_f(g.w); }
+            if (mode == 2) { v.x *= silu_f(g.x); v.y *= silu_f(g.y); v.z *= silu_f(g.z); v.w *= silu_f(g.w); }
             orow[i] = from_float<AT>(v.x); orow[i + 1] = from_float<AT>(v.y);
             orow[i + 2] = from_float<AT>(v.z); orow[i + 3] = from_float<AT>(v.w);
         }
@@ -514,6 +543,7 @@ gated_group_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict_
             if (mode == 0) v *= silu_f(gr[i]);
             v = v * rr * to_float(w[(c0 + i) % wlen]);
             if (mode == 1) v *= sigmoid_f(gr[i]);
+            if (mode == 2) v *= silu_f(gr[i]);
             orow[i] = from_float<AT>(v);
         }
     }
@@ -525,9 +555,11 @@ using namespace mi;
 
 extern "C" {
 
-int mi_causal_conv_silu(const float* x, int ldx, const void* w, const void* bias, int wdtype, float* state,
-                        int64_t state_stride, const int* q_start, const int* req_of_token, const int* state_slot,
-                        float* out, int ld_out, int C, int taps, int T, int B, cudaStream_t stream) {
+// form 0: silu(conv(x) + bias), float out; form 1: x + conv(x) in the type `odtype`
+static int launch_causal_conv(const float* x, int ldx, const void* w, const void* bias, int wdtype, float* state,
+                              int64_t state_stride, const int* q_start, const int* req_of_token, const int* state_slot,
+                              void* out, int odtype, int ld_out, int C, int taps, int T, int B, bool residual,
+                              cudaStream_t stream) {
     if (T <= 0 || C <= 0) return kOk;
     if (taps < 1 || taps > kMaxTaps) {
         set_last_error("causal convolution: %d taps are outside [1, %d]", taps, kMaxTaps);
@@ -541,24 +573,47 @@ int mi_causal_conv_silu(const float* x, int ldx, const void* w, const void* bias
     if (ty > 65535) ty = 65535;
     const bool vec4 = C % 4 == 0 && ldx % 4 == 0 && ld_out % 4 == 0 && state_stride % 4 == 0 &&
                       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(state)) & 15) == 0;
-    if (vec4) {
-        MI_DISPATCH_1(wdtype, WT,
-            launch_dependent(causal_conv_silu_vec4_kernel<WT>, dim3((C / 4 + 127) / 128, ty), dim3(128), 0, stream, x, ldx,
-                             (const WT*)w, (const WT*)bias, (const float*)state, state_stride, q_start, req_of_token,
-                             state_slot, out, ld_out, C, taps, T));
-    } else {
-        MI_DISPATCH_1(wdtype, WT,
-            launch_dependent(causal_conv_silu_kernel<WT>, dim3(cb, ty), dim3(256), 0, stream, x, ldx, (const WT*)w,
-                             (const WT*)bias, (const float*)state, state_stride, q_start, req_of_token, state_slot, out,
-                             ld_out, C, taps, T));
-    }
+#define MI_CONV_LAUNCH(OT, RES)                                                                                       \
+    do {                                                                                                              \
+        if (vec4) {                                                                                                   \
+            MI_DISPATCH_1(wdtype, WT,                                                                                 \
+                launch_dependent(causal_conv_silu_vec4_kernel<WT, OT, RES>, dim3((C / 4 + 127) / 128, ty), dim3(128), 0, \
+                                 stream, x, ldx, (const WT*)w, (const WT*)bias, (const float*)state, state_stride,    \
+                                 q_start, req_of_token, state_slot, (OT*)out, ld_out, C, taps, T));                   \
+        } else {                                                                                                      \
+            MI_DISPATCH_1(wdtype, WT,                                                                                 \
+                launch_dependent(causal_conv_silu_kernel<WT, OT, RES>, dim3(cb, ty), dim3(256), 0, stream, x, ldx,     \
+                                 (const WT*)w, (const WT*)bias, (const float*)state, state_stride, q_start,           \
+                                 req_of_token, state_slot, (OT*)out, ld_out, C, taps, T));                            \
+        }                                                                                                             \
+    } while (0)
+    if (!residual) MI_CONV_LAUNCH(float, false);
+    else if (odtype == kBF16) MI_CONV_LAUNCH(__nv_bfloat16, true);
+    else if (odtype == kF32) MI_CONV_LAUNCH(float, true);
+    else return kBadDType;
+#undef MI_CONV_LAUNCH
     int launched = 1;
     if (taps > 1) {
         launch_dependent(conv_state_update_kernel, dim3(cb, B), dim3(256), 0, stream, x, ldx, state, state_stride,
                          q_start, state_slot, C, taps);
         launched = 2;
     }
-    return finish_launch("causal_conv_silu", launched);
+    return finish_launch(residual ? "causal_conv_residual" : "causal_conv_silu", launched);
+}
+
+int mi_causal_conv_silu(const float* x, int ldx, const void* w, const void* bias, int wdtype, float* state,
+                        int64_t state_stride, const int* q_start, const int* req_of_token, const int* state_slot,
+                        float* out, int ld_out, int C, int taps, int T, int B, cudaStream_t stream) {
+    return launch_causal_conv(x, ldx, w, bias, wdtype, state, state_stride, q_start, req_of_token, state_slot, out,
+                              kF32, ld_out, C, taps, T, B, false, stream);
+}
+
+// out[t, c] = x[t, c] + sum_j w[c, j] * x(t - (taps-1-j), c) in the type `odtype`; state as above
+int mi_causal_conv_residual(const float* x, int ldx, const void* w, int wdtype, float* state, int64_t state_stride,
+                            const int* q_start, const int* req_of_token, const int* state_slot, void* out, int odtype,
+                            int ld_out, int C, int taps, int T, int B, cudaStream_t stream) {
+    return launch_causal_conv(x, ldx, w, nullptr, wdtype, state, state_stride, q_start, req_of_token, state_slot, out,
+                              odtype, ld_out, C, taps, T, B, true, stream);
 }
 
 #define MI_SCAN_DISPATCH(rows, ...)                                                     \
@@ -571,26 +626,46 @@ int mi_causal_conv_silu(const float* x, int ldx, const void* w, const void* bias
 // floats of one (token, head) of the scratch that mi_delta_scan needs: T * H * this many
 int mi_delta_scan_prep_row(int d) { return 3 * (d <= 64 ? 64 : (d <= 128 ? 128 : 256)) + 4; }
 
-int mi_delta_scan(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
-                  const float* a_log, const float* dt_bias, float* state, int64_t state_stride, const int* q_start,
-                  const int* state_slot, float* out, float* prep, int T, int B, int H, int G, int d, int dv,
-                  float q_scale, cudaStream_t stream) {
+// form: see delta_prepare_kernel (0 and 1: the delta rule; 2: gated linear attention, which reads neither
+// beta_raw nor a_log); tau: form 2 only
+int mi_delta_scan_form(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
+                       const float* a_log, const float* dt_bias, float* state, int64_t state_stride,
+                       const int* q_start, const int* state_slot, float* out, float* prep, int T, int B, int H, int G,
+                       int d, int dv, float q_scale, int form, float tau, cudaStream_t stream) {
     if (B <= 0 || T <= 0) return kOk;
     if (d < 1 || d > 256 || dv < 1) { set_last_error("delta rule: key size %d outside [1, 256] or value size %d", d, dv); return kBadShape; }
     if (G < 1 || H % G) { set_last_error("delta rule: %d heads are not a multiple of %d key heads", H, G); return kBadShape; }
     if (B > 65535 || H > 65535) { set_last_error("delta rule: batch %d or heads %d exceed the grid limit", B, H); return kBadShape; }
     if (!prep || (reinterpret_cast<uintptr_t>(prep) & 15)) { set_last_error("delta rule: the scratch is missing or not 16-byte aligned"); return kBadShape; }
+    if (form < 0 || form > 2 || (form == kSigmoidDecay && !(tau > 0.f)) || (form != kSigmoidDecay && (!beta_raw || !a_log))) {
+        set_last_error("delta rule: form %d with tau %g, or a form that lacks its write strengths or decay rates", form, (double)tau);
+        return kBadShape;
+    }
     const int DP = d <= 64 ? 64 : (d <= 128 ? 128 : 256);
     launch_dependent(delta_prepare_kernel, dim3(T, H), dim3(128), 0, stream, qkv, ld_qkv, beta_raw, ld_beta, a_raw, ld_a,
-                     a_log, dt_bias, prep, H, G, d, DP, q_scale);
+                     a_log, dt_bias, prep, H, G, d, DP, q_scale, form, tau);
     const dim3 grid((dv + kScanCols - 1) / kScanCols, H, B);
     MI_SCAN_DISPATCH(d, {
         const size_t smem = sizeof(float) * (2 * kScanChunk * (3 * RP * kScanLanes + 4 + kScanCols) + kScanChunk * kScanCols);
-        cudaFuncSetAttribute(delta_scan_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_dependent(delta_scan_kernel<RP>, grid, dim3(128), smem, stream, qkv, ld_qkv, (int64_t)2 * G * d,
-                         (const float*)prep, state, state_stride, q_start, state_slot, out, H, d, dv);
+        if (form == kSigmoidDecay) {
+            cudaFuncSetAttribute(delta_scan_kernel<RP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            launch_dependent(delta_scan_kernel<RP, false>, grid, dim3(128), smem, stream, qkv, ld_qkv, (int64_t)2 * G * d,
+                             (const float*)prep, state, state_stride, q_start, state_slot, out, H, d, dv);
+        } else {
+            cudaFuncSetAttribute(delta_scan_kernel<RP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            launch_dependent(delta_scan_kernel<RP, true>, grid, dim3(128), smem, stream, qkv, ld_qkv, (int64_t)2 * G * d,
+                             (const float*)prep, state, state_stride, q_start, state_slot, out, H, d, dv);
+        }
     });
     return finish_launch("delta_scan", 2);
+}
+
+int mi_delta_scan(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
+                  const float* a_log, const float* dt_bias, float* state, int64_t state_stride, const int* q_start,
+                  const int* state_slot, float* out, float* prep, int T, int B, int H, int G, int d, int dv,
+                  float q_scale, cudaStream_t stream) {
+    return mi_delta_scan_form(qkv, ld_qkv, beta_raw, ld_beta, a_raw, ld_a, a_log, dt_bias, state, state_stride, q_start,
+                              state_slot, out, prep, T, B, H, G, d, dv, q_scale, kDecayPerChannel, 1.0f, stream);
 }
 
 int mi_ssd_scan(const float* xbc, int ld_x, const float* dt_raw, int ld_dt, const float* dt_bias, const float* a_log,
@@ -614,7 +689,7 @@ int mi_ssd_scan(const float* xbc, int ld_x, const float* dt_raw, int ld_dt, cons
 int mi_gated_group_rmsnorm(const float* y, const float* gate, int ld_gate, const void* w, int wdtype, int wlen,
                            void* out, int adtype, int T, int n, int groups, int mode, float eps, cudaStream_t stream) {
     if (T <= 0 || n <= 0) return kOk;
-    if (groups < 1 || n % groups || groups > 65535 || wlen < 1 || (mode != 0 && mode != 1)) {
+    if (groups < 1 || n % groups || groups > 65535 || wlen < 1 || (mode < 0 || mode > 2)) {
         set_last_error("gated group norm: %d columns in %d groups, weight of %d, mode %d", n, groups, wlen, mode);
         return kBadShape;
     }

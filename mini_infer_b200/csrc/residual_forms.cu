@@ -9,6 +9,8 @@
 //   concat_cast           out[t] = [hidden[t] + a[t] + b[t] | other[t]] in the activation type: the input
 //                         of a projection that reads the residual beside a second stream
 //   rows_plus_vec         hidden[t] = y[t] + vec: a projection's result becomes the residual, plus one row
+//   group_rmsnorm         out[t] = hidden[t] / rms * w with the root mean square taken over each of `groups` equal
+//                         consecutive parts of the row by itself (out_norm_add takes `groups` as well)
 //   out_norm_add          hidden[t] += mult * y[t] / rms(y[t]) * w, and the new row once more in the activation
 //                         type: a block whose parts read the residual itself and whose OUTPUT is normalised;
 //                         y may be a sum of rows that is formed here and never written out
@@ -161,26 +163,28 @@ __device__ __forceinline__ float row_sum_at(const RowSum& s, int64_t t, int i, i
     return v;
 }
 
-// One block per row.  The sum of squares runs in an order that depends on H only.
+// One block per row and group of columns (gs = H / groups columns from blockIdx.y * gs on; one group: the whole
+// row).  The sum of squares runs in an order that depends on gs only.
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(256)
 out_norm_add_kernel(float* __restrict__ hidden, RowSum s, const WT* __restrict__ w, AT* __restrict__ x_out, int H,
-                    float eps, float mult) {
-    extern __shared__ float yrow[];             // [H] when it fits (else the sum is formed twice)
+                    float eps, float mult, int gs) {
+    extern __shared__ float yrow[];             // [gs] when it fits (else the sum is formed twice)
     __shared__ float scratch[32];
     wait_for_earlier_kernels();
     const int64_t t = blockIdx.x;
-    const bool staged = H <= 8192;
+    const int c0 = blockIdx.y * gs;
+    const bool staged = gs <= 8192;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    for (int i = c0 + threadIdx.x; i < c0 + gs; i += blockDim.x) {
         const float v = row_sum_at(s, t, i, H);
-        if (staged) yrow[i] = v;
+        if (staged) yrow[i - c0] = v;
         ss += v * v;
     }
     ss = block_sum(ss, scratch);
-    const float rr = 1.0f / sqrtf(ss / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = staged ? yrow[i] : row_sum_at(s, t, i, H);
+    const float rr = 1.0f / sqrtf(ss / (float)gs + eps);
+    for (int i = c0 + threadIdx.x; i < c0 + gs; i += blockDim.x) {
+        const float v = staged ? yrow[i - c0] : row_sum_at(s, t, i, H);
         const float h = hidden[t * H + i] + mult * (v * rr * to_float(w[i]));
         hidden[t * H + i] = h;
         if (x_out) x_out[t * H + i] = from_float<AT>(h);
@@ -196,16 +200,17 @@ __device__ __forceinline__ void axpy4(float4& a, float w, const float4& x) {
 template <typename AT, typename WT, int VPT>
 __global__ void __launch_bounds__(256)
 out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restrict__ w, AT* __restrict__ x_out, int H,
-                        float eps, float mult) {
+                        float eps, float mult, int gs) {
     __shared__ float scratch[32];
     wait_for_earlier_kernels();
     const int64_t t = blockIdx.x;
-    const int nv = H >> 2;
+    const int c0 = blockIdx.y * gs;             // this block's group of gs columns (one group: the whole row)
+    const int nv = gs >> 2;
     float4 y[VPT];
 #pragma unroll
     for (int j = 0; j < VPT; ++j) y[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (s.y) {
-        const float4* yv = reinterpret_cast<const float4*>(s.y + t * H);
+        const float4* yv = reinterpret_cast<const float4*>(s.y + t * H + c0);
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int i = threadIdx.x + 256 * j;
@@ -215,7 +220,7 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
         for (int k = 0; k < s.K; ++k) {
             const int64_t r = s.index ? s.index[t * s.K + k] : t * s.K + k;
             const float wk = s.wk ? s.wk[t * s.K + k] : 1.0f;
-            const float4* rv = reinterpret_cast<const float4*>(s.rows + r * H);
+            const float4* rv = reinterpret_cast<const float4*>(s.rows + r * H + c0);
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const int i = threadIdx.x + 256 * j;
@@ -224,7 +229,7 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
         }
         if (s.extra) {
             const float g = s.scale[t];
-            const float4* ev = reinterpret_cast<const float4*>(s.extra + t * H);
+            const float4* ev = reinterpret_cast<const float4*>(s.extra + t * H + c0);
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const int i = threadIdx.x + 256 * j;
@@ -233,7 +238,7 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
         }
     }
     // the residual row is on its way while the squares are added
-    float4* hv = reinterpret_cast<float4*>(hidden + t * H);
+    float4* hv = reinterpret_cast<float4*>(hidden + t * H + c0);
     float4 h[VPT];
     float ss = 0.f;
 #pragma unroll
@@ -246,12 +251,12 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
         ss += y[j].w * y[j].w;
     }
     ss = block_sum(ss, scratch);
-    const float rr = 1.0f / sqrtf(ss / (float)H + eps);
+    const float rr = 1.0f / sqrtf(ss / (float)gs + eps);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int i = threadIdx.x + 256 * j;
         if (i < nv) {
-            const int c = 4 * i;
+            const int c = c0 + 4 * i;
             h[j].x += mult * (y[j].x * rr * to_float(w[c]));
             h[j].y += mult * (y[j].y * rr * to_float(w[c + 1]));
             h[j].z += mult * (y[j].z * rr * to_float(w[c + 2]));
@@ -259,6 +264,44 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
             hv[i] = h[j];
             if (x_out) store4(x_out + t * H + c, h[j]);
         }
+    }
+}
+
+// out[n, :] = x[row, :] / rms * w with the root mean square of each group of gs columns by itself; one block per
+// (row, group).  `rows` (or null) picks the rows of x that are wanted.  The squares are added per thread in
+// ascending order and then over the block: an order that depends on gs only.
+template <typename OT, typename WT>
+__global__ void __launch_bounds__(256)
+group_rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const WT* __restrict__ w,
+                     OT* __restrict__ out, int H, int gs, float eps, bool vec) {
+    __shared__ float scratch[32];
+    wait_for_earlier_kernels();
+    const int64_t n = blockIdx.x, t = rows ? rows[n] : n;
+    const int c0 = blockIdx.y * gs;
+    const float* xr = x + t * H + c0;
+    OT* orow = out + n * H + c0;
+    float ss = 0.f;
+    if (vec) {
+        for (int i = 4 * threadIdx.x; i < gs; i += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + i);
+            ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = xr[i]; ss += v * v; }
+    }
+    ss = block_sum(ss, scratch);
+    const float rr = 1.0f / sqrtf(ss / (float)gs + eps);
+    if (vec) {
+        for (int i = 4 * threadIdx.x; i < gs; i += 4 * blockDim.x) {
+            float4 v = *reinterpret_cast<const float4*>(xr + i);
+            v.x = v.x * rr * to_float(w[c0 + i]);
+            v.y = v.y * rr * to_float(w[c0 + i + 1]);
+            v.z = v.z * rr * to_float(w[c0 + i + 2]);
+            v.w = v.w * rr * to_float(w[c0 + i + 3]);
+            store4(orow + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) orow[i] = from_float<OT>(xr[i] * rr * to_float(w[c0 + i]));
     }
 }
 
@@ -340,10 +383,52 @@ int mi_rows_plus_vec(float* hidden, const float* y, const void* vec, int wdtype,
     return finish_launch("rows_plus_vec");
 }
 
+int mi_group_rmsnorm(const float* x, const int* rows, const void* w, int wdtype, void* out, int odtype, int n, int H,
+                     int groups, float eps, cudaStream_t stream) {
+    if (n <= 0 || H <= 0) return kOk;
+    if (groups < 1 || H % groups || groups > 65535) {
+        set_last_error("group norm: %d columns do not split into %d groups", H, groups);
+        return kBadShape;
+    }
+    const int gs = H / groups;
+    const bool vec = gs % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int work = vec ? gs / 4 : gs;
+    int threads = 32;
+    while (threads < work && threads < 256) threads *= 2;
+    MI_DISPATCH_2(odtype, OT, wdtype, WT,
+        launch_dependent(group_rmsnorm_kernel<OT, WT>, dim3(n, groups), dim3(threads), 0, stream, x, rows,
+                         (const WT*)w, (OT*)out, H, gs, eps, vec));
+    return finish_launch("group_rmsnorm");
+}
+
+static int out_norm_add_groups(float* hidden, const float* y, const float* rows, const int* index, const float* wk,
+                               const float* extra, const float* scale, int K, const void* w, int wdtype, void* x_out,
+                               int adtype, int T, int H, float eps, float mult, int groups, cudaStream_t stream);
+
 int mi_out_norm_add(float* hidden, const float* y, const float* rows, const int* index, const float* wk,
                     const float* extra, const float* scale, int K, const void* w, int wdtype, void* x_out, int adtype,
                     int T, int H, float eps, float mult, cudaStream_t stream) {
+    return out_norm_add_groups(hidden, y, rows, index, wk, extra, scale, K, w, wdtype, x_out, adtype, T, H, eps, mult,
+                               1, stream);
+}
+
+// the same with the root mean square of each of `groups` equal consecutive parts of the row by itself
+int mi_out_norm_add_groups(float* hidden, const float* y, const float* rows, const int* index, const float* wk,
+                           const float* extra, const float* scale, int K, const void* w, int wdtype, void* x_out,
+                           int adtype, int T, int H, float eps, float mult, int groups, cudaStream_t stream) {
+    return out_norm_add_groups(hidden, y, rows, index, wk, extra, scale, K, w, wdtype, x_out, adtype, T, H, eps, mult,
+                               groups, stream);
+}
+
+static int out_norm_add_groups(float* hidden, const float* y, const float* rows, const int* index, const float* wk,
+                               const float* extra, const float* scale, int K, const void* w, int wdtype, void* x_out,
+                               int adtype, int T, int H, float eps, float mult, int groups, cudaStream_t stream) {
     if (T <= 0 || H <= 0) return kOk;
+    if (groups < 1 || H % groups || groups > 65535) {
+        set_last_error("out_norm_add: %d columns do not split into %d groups", H, groups);
+        return kBadShape;
+    }
+    const int gs = H / groups;
     if (!y && (!rows || K < 1)) { set_last_error("out_norm_add: neither a tensor nor rows to add"); return kBadShape; }
     if ((extra == nullptr) != (scale == nullptr)) {
         set_last_error("out_norm_add: the extra term and its scale come together");
@@ -353,22 +438,22 @@ int mi_out_norm_add(float* hidden, const float* y, const float* rows, const int*
     const uintptr_t ptrs = reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(y) |
                            reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(extra) |
                            reinterpret_cast<uintptr_t>(x_out);
-    if (H % 4 == 0 && H <= 8192 && (ptrs & 15) == 0) {
+    if (gs % 4 == 0 && gs <= 8192 && (ptrs & 15) == 0) {
 #define MI_OUT_NORM_VEC(VPT)                                                                                         \
     MI_DISPATCH_2(adtype, AT, wdtype, WT,                                                                            \
-        launch_dependent(out_norm_add_vec_kernel<AT, WT, VPT>, dim3(T), dim3(256), 0, stream, hidden, s,             \
-                         (const WT*)w, (AT*)x_out, H, eps, mult))
-        if (H <= 1024) { MI_OUT_NORM_VEC(1); }
-        else if (H <= 2048) { MI_OUT_NORM_VEC(2); }
-        else if (H <= 4096) { MI_OUT_NORM_VEC(4); }
+        launch_dependent(out_norm_add_vec_kernel<AT, WT, VPT>, dim3(T, groups), dim3(256), 0, stream, hidden, s,     \
+                         (const WT*)w, (AT*)x_out, H, eps, mult, gs))
+        if (gs <= 1024) { MI_OUT_NORM_VEC(1); }
+        else if (gs <= 2048) { MI_OUT_NORM_VEC(2); }
+        else if (gs <= 4096) { MI_OUT_NORM_VEC(4); }
         else { MI_OUT_NORM_VEC(8); }
 #undef MI_OUT_NORM_VEC
         return finish_launch("out_norm_add");
     }
-    const size_t smem = H <= 8192 ? sizeof(float) * H : 0;
+    const size_t smem = gs <= 8192 ? sizeof(float) * gs : 0;
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
-        launch_dependent(out_norm_add_kernel<AT, WT>, dim3(T), dim3(256), smem, stream, hidden, s, (const WT*)w,
-                         (AT*)x_out, H, eps, mult));
+        launch_dependent(out_norm_add_kernel<AT, WT>, dim3(T, groups), dim3(256), smem, stream, hidden, s, (const WT*)w,
+                         (AT*)x_out, H, eps, mult, gs));
     return finish_launch("out_norm_add");
 }
 

@@ -1,3 +1,3 @@
 """Architectures this engine builds.  Importing the package registers them by name."""
 
-from . import nipapel, qwen2_moe, tofinex, vizalix  # noqa: F401
+from . import bogetar, nipapel, qwen2_moe, tofinex, vizalix  # noqa: F401

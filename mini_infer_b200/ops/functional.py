@@ -490,15 +490,24 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return out
 
 
-def _selection_mode(norm_topk: bool, scoring: str) -> int:
+def _selection_mode(norm_topk: bool, scoring: str, groups: Optional[Tuple[int, int]] = None) -> int:
+    """The switches of the experts' selection as one word: renormalised weights, logistic scores, and
+    ``groups = (count, keep)``: the experts form ``count`` equal groups of neighbours, and only those of the
+    ``keep`` groups with the largest best score can be chosen."""
     if scoring not in ("softmax", "sigmoid"):
         raise ValueError(f"router scoring '{scoring}' is not 'softmax' or 'sigmoid'")
-    return int(bool(norm_topk)) | (2 if scoring == "sigmoid" else 0)
+    mode = int(bool(norm_topk)) | (2 if scoring == "sigmoid" else 0)
+    if groups is not None and groups[0] > 1 and groups[1] < groups[0]:
+        count, keep = int(groups[0]), int(groups[1])
+        if scoring != "softmax" or not 1 <= keep or count > 0xfff:
+            raise ValueError(f"router: {keep} of {count} expert groups with '{scoring}' scores is not built")
+        mode |= (count << 8) | (keep << 20)
+    return mode
 
 
 def moe_router(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
                norm_topk: bool, want_probs: bool = False, bias: Optional[torch.Tensor] = None,
-               scoring: str = "softmax"
+               scoring: str = "softmax", groups: Optional[Tuple[int, int]] = None
                ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Router of one layer.  Returns ``(idx [T,K] int32, w [T,K] f32, gate [T] f32 | None, probs | None)``.
     ``bias`` (float32 ``[E]``) is added to the logits before the softmax and the choice.  ``scoring``
@@ -520,8 +529,8 @@ def moe_router(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[
     z = torch.empty(T, E + 1, dtype=F32, device=dev)
     check(library().mi_moe_router(_ptr(x), _code(x, "moe_router x"), _ptr(router_w), _ptr(shared_gate_w),
                                   _code(router_w, "moe_router weight"), _ptr(z), _ptr(idx), _ptr(w), _ptr(gate),
-                                  _ptr(probs), T, H, E, int(top_k), _selection_mode(norm_topk, scoring), _ptr(bias),
-                                  _stream()),
+                                  _ptr(probs), T, H, E, int(top_k), _selection_mode(norm_topk, scoring, groups),
+                                  _ptr(bias), _stream()),
           "moe_router")
     return idx, w, gate, probs
 
@@ -551,7 +560,8 @@ def route_small_max_tokens() -> int:
 
 def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
                     norm_topk: bool, ticket: torch.Tensor, want_probs: bool = False, permute: bool = True,
-                    bias: Optional[torch.Tensor] = None, scoring: str = "softmax"):
+                    bias: Optional[torch.Tensor] = None, scoring: str = "softmax",
+                    groups: Optional[Tuple[int, int]] = None):
     """:func:`moe_router` and (with ``permute``) :func:`moe_permute` of a step of a few tokens in
     one launch.
 
@@ -586,8 +596,8 @@ def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Opti
     check(library().mi_moe_route_small(
         _ptr(x), _code(x, "moe_route_small x"), _ptr(router_w), _ptr(shared_gate_w),
         _code(router_w, "moe_route_small weight"), _ptr(z), _ptr(ticket), _ptr(idx), _ptr(w), _ptr(gate), _ptr(probs),
-        _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T, H, E, int(top_k), _selection_mode(norm_topk, scoring),
-        _ptr(bias), _stream()), "moe_route_small")
+        _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T, H, E, int(top_k),
+        _selection_mode(norm_topk, scoring, groups), _ptr(bias), _stream()), "moe_route_small")
     return idx, w, gate, probs, offsets, sorted_token, inv_perm
 
 
@@ -1023,9 +1033,10 @@ def add2_rmsnorm_scalar(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Opti
 
 
 def out_norm_add(hidden: torch.Tensor, y, weight: torch.Tensor, eps: float, mult: float,
-                 out_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
+                 out_dtype: Optional[torch.dtype], groups: int = 1) -> Optional[torch.Tensor]:
     """``hidden += mult * y / rms(y) * weight`` row by row (float32), and the new rows once more in ``out_dtype``
-    (None: not wanted).  ``y`` is a float32 tensor ``[T, H]`` or the tuple ``(rows, index, weights, extra,
+    (None: not wanted).  With ``groups`` the root mean square is taken over each of that many equal consecutive
+    parts of a row by itself.  ``y`` is a float32 tensor ``[T, H]`` or the tuple ``(rows, index, weights, extra,
     scale)`` of a sum of rows, ``y[t] = sum_k weights[t, k] rows[index[t, k]] + scale[t] extra[t]`` (``weights``
     None: ones, then ``index`` gives the number of slots; ``index`` None: rows in order), which is formed inside
     the kernel and never written out."""
@@ -1053,10 +1064,39 @@ def out_norm_add(hidden: torch.Tensor, y, weight: torch.Tensor, eps: float, mult
         if DEBUG_BOUNDS:
             _dbg_range(index, 0, rows.shape[0], "out_norm_add index")
     out = torch.empty(T, H, dtype=out_dtype, device=hidden.device) if out_dtype is not None else None
+    if groups != 1:
+        if groups < 1 or H % groups:
+            raise ValueError(f"out_norm_add: rows of {H} do not split into {groups} groups")
+        check(library().mi_out_norm_add_groups(
+            _ptr(hidden), _ptr(yt), _ptr(rows), _ptr(index), _ptr(wk), _ptr(extra), _ptr(scale), K, _ptr(weight),
+            _code(weight, "out_norm_add weight"), _ptr(out), _CODES[out_dtype] if out_dtype is not None else 0, T, H,
+            float(eps), float(mult), int(groups), _stream()), "out_norm_add")
+        return out
     check(library().mi_out_norm_add(_ptr(hidden), _ptr(yt), _ptr(rows), _ptr(index), _ptr(wk), _ptr(extra), _ptr(scale),
                                     K, _ptr(weight), _code(weight, "out_norm_add weight"), _ptr(out),
                                     _CODES[out_dtype] if out_dtype is not None else 0, T, H, float(eps), float(mult),
                                     _stream()), "out_norm_add")
+    return out
+
+
+def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype,
+                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x / rms * weight`` of float32 rows ``[T, H]`` with the root mean square (``eps`` inside the root) taken
+    over each of ``groups`` equal consecutive parts of a row by itself; ``rows`` (int32) picks the rows that are
+    wanted.  Returns ``[T or len(rows), H]`` in ``out_dtype``."""
+    _chk(x, "group_rmsnorm x", F32)
+    T, H = x.shape
+    _chk(weight, "group_rmsnorm weight", None, (H,))
+    _chk(rows, "group_rmsnorm rows", I32)
+    if groups < 1 or H % groups:
+        raise ValueError(f"group_rmsnorm: rows of {H} do not split into {groups} groups")
+    n = rows.numel() if rows is not None else T
+    if DEBUG_BOUNDS:
+        _dbg_range(rows, 0, T, "group_rmsnorm rows")
+    out = torch.empty(n, H, dtype=out_dtype, device=x.device)
+    check(library().mi_group_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight), _code(weight, "group_rmsnorm weight"), _ptr(out),
+                                     _code(out, "group_rmsnorm out"), n, H, int(groups), float(eps), _stream()),
+          "group_rmsnorm")
     return out
 
 
@@ -1150,13 +1190,52 @@ def causal_conv_silu(x: torch.Tensor, col0: int, channels: int, w: torch.Tensor,
     return out
 
 
-def delta_scan(qkv: torch.Tensor, beta_raw: torch.Tensor, beta_col: int, a_raw: torch.Tensor, a_col: int,
-               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, state_offset: int,
+def causal_conv_residual(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, state_offset: int,
+                         q_start: torch.Tensor, req_of_token: torch.Tensor, state_slot: torch.Tensor,
+                         out_dtype: torch.dtype) -> torch.Tensor:
+    """``x + conv(x)`` of float32 rows ``[T, C]``: a causal convolution over time per channel without an
+    activation, ``conv(x)_t = sum_j w[:, j] x_(t - taps + 1 + j)`` with ``w [C, taps]``.  The ``taps - 1`` rows
+    before a request's portion come from ``state[slot, state_offset : state_offset + (taps-1)*C]`` (time-major),
+    which is brought up to date afterwards.  Returns ``[T, C]`` in ``out_dtype``."""
+    _chk(x, "causal_conv_residual x", F32)
+    T, C = x.shape
+    _chk(w, "causal_conv_residual w", None, (C, None))
+    taps = w.shape[1]
+    _chk(state, "causal_conv_residual state", F32)
+    if state.dim() != 2 or state_offset + (taps - 1) * C > state.shape[1]:
+        raise ValueError("causal_conv_residual: state section out of range")
+    B = state_slot.numel()
+    _chk(q_start, "causal_conv_residual q_start", I32, (B + 1,))
+    _chk(req_of_token, "causal_conv_residual req_of_token", I32, (T,))
+    _chk(state_slot, "causal_conv_residual state_slot", I32, (B,))
+    if DEBUG_BOUNDS:
+        _dbg_range(state_slot, 0, state.shape[0], "causal_conv_residual state_slot")
+        _dbg_range(req_of_token, 0, B, "causal_conv_residual req_of_token")
+    out = torch.empty(T, C, dtype=out_dtype, device=x.device)
+    check(library().mi_causal_conv_residual(_ptr(x), C, _ptr(w), _code(w, "causal_conv_residual w"),
+                                            state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start),
+                                            _ptr(req_of_token), _ptr(state_slot), _ptr(out),
+                                            _code(out, "causal_conv_residual out"), C, C, taps, T, B, _stream()),
+          "causal_conv_residual")
+    return out
+
+
+DELTA_FORMS = {"channel_decay": 0, "head_decay": 1, "sigmoid_decay": 2}
+
+
+def delta_scan(qkv: torch.Tensor, beta_raw: Optional[torch.Tensor], beta_col: int, a_raw: torch.Tensor, a_col: int,
+               a_log: Optional[torch.Tensor], dt_bias: torch.Tensor, state: torch.Tensor, state_offset: int,
                q_start: torch.Tensor, state_slot: torch.Tensor, heads: int, key_heads: int, d: int, dv: int,
-               q_scale: float) -> torch.Tensor:
+               q_scale: float, form: str = "channel_decay", tau: float = 1.0) -> torch.Tensor:
     """Gated delta rule with a decay per head and key channel, token by token over every request's portion.
 
-    ``qkv`` float32 ``[T, 2*key_heads*d + heads*dv]`` (q | k | v after their convolutions); ``beta_raw`` holds
+    ``form`` ``head_decay``: ONE decay per head (``a_raw`` holds ``heads`` columns and ``dt_bias`` ``heads``
+    numbers).  ``form`` ``sigmoid_decay``: gated linear attention, ``S <- diag(g) S + k v^T; o = S^T q`` with
+    q (times ``q_scale``) and k as they are and ``g = sigmoid(a + dt_bias)^(1 / tau)`` per head and key channel;
+    ``beta_raw`` and ``a_log`` are not read.
+
+    ``qkv`` float32 ``[T, 2*key_heads*d + heads*dv]`` (q | k | v after their convolutions; the rows may go on
+    with columns that are not read); ``beta_raw`` holds
     the ``heads`` write strengths before the sigmoid from column ``beta_col``; ``a_raw`` the ``heads*d`` decay
     inputs before ``dt_bias`` and the softplus from column ``a_col``.  Per head, with unit q (times
     ``q_scale``) and unit k: ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` where
@@ -1164,17 +1243,22 @@ def delta_scan(qkv: torch.Tensor, beta_raw: torch.Tensor, beta_col: int, a_raw: 
     ``state[slot, state_offset:]``.  Returns ``o`` float32 ``[T, heads*dv]``."""
     _chk(qkv, "delta_scan qkv", F32)
     T = qkv.shape[0]
-    if qkv.shape[1] != 2 * key_heads * d + heads * dv:
+    if qkv.shape[1] < 2 * key_heads * d + heads * dv:
         raise ValueError("delta_scan: the rows of qkv do not hold q, k and v of the given sizes")
+    if form not in DELTA_FORMS:
+        raise ValueError(f"delta_scan: form '{form}' is not one of {sorted(DELTA_FORMS)}")
+    n_decay = heads if form == "head_decay" else heads * d
     _chk(beta_raw, "delta_scan beta_raw", F32)
     _chk(a_raw, "delta_scan a_raw", F32)
     _chk(a_log, "delta_scan a_log", F32, (heads,))
-    _chk(dt_bias, "delta_scan dt_bias", F32, (heads * d,))
+    _chk(dt_bias, "delta_scan dt_bias", F32, (n_decay,))
     _chk(state, "delta_scan state", F32)
     B = state_slot.numel()
     _chk(q_start, "delta_scan q_start", I32, (B + 1,))
     _chk(state_slot, "delta_scan state_slot", I32, (B,))
-    if (beta_col + heads > beta_raw.shape[1] or a_col + heads * d > a_raw.shape[1]
+    if form != "sigmoid_decay" and (beta_raw is None or a_log is None):
+        raise ValueError("delta_scan: the delta rule needs its write strengths and decay rates")
+    if ((beta_raw is not None and beta_col + heads > beta_raw.shape[1]) or a_col + n_decay > a_raw.shape[1]
             or state_offset + heads * d * dv > state.shape[1]):
         raise ValueError("delta_scan: columns or state section out of range")
     if DEBUG_BOUNDS:
@@ -1182,10 +1266,18 @@ def delta_scan(qkv: torch.Tensor, beta_raw: torch.Tensor, beta_col: int, a_raw: 
     out = torch.empty(T, heads * dv, dtype=F32, device=qkv.device)
     # unit vectors, decays and write strengths of all tokens, made ready by a kernel before the walk
     prep = torch.empty(T * heads * library().mi_delta_scan_prep_row(d), dtype=F32, device=qkv.device)
-    check(library().mi_delta_scan(_ptr(qkv), qkv.shape[1], beta_raw.data_ptr() + 4 * beta_col, beta_raw.shape[1],
-                                  a_raw.data_ptr() + 4 * a_col, a_raw.shape[1], _ptr(a_log), _ptr(dt_bias),
-                                  state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start), _ptr(state_slot),
-                                  _ptr(out), _ptr(prep), T, B, heads, key_heads, d, dv, float(q_scale), _stream()),
+    if form == "channel_decay":
+        check(library().mi_delta_scan(_ptr(qkv), qkv.shape[1], beta_raw.data_ptr() + 4 * beta_col, beta_raw.shape[1],
+                                      a_raw.data_ptr() + 4 * a_col, a_raw.shape[1], _ptr(a_log), _ptr(dt_bias),
+                                      state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start),
+                                      _ptr(state_slot), _ptr(out), _ptr(prep), T, B, heads, key_heads, d, dv,
+                                      float(q_scale), _stream()), "delta_scan")
+        return out
+    check(library().mi_delta_scan_form(
+        _ptr(qkv), qkv.shape[1], None if beta_raw is None else beta_raw.data_ptr() + 4 * beta_col,
+        0 if beta_raw is None else beta_raw.shape[1], a_raw.data_ptr() + 4 * a_col, a_raw.shape[1], _ptr(a_log),
+        _ptr(dt_bias), state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start), _ptr(state_slot), _ptr(out),
+        _ptr(prep), T, B, heads, key_heads, d, dv, float(q_scale), DELTA_FORMS[form], float(tau), _stream()),
           "delta_scan")
     return out
 
@@ -1222,10 +1314,11 @@ def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_col: int, dt_bias: torc
 
 
 def gated_group_rmsnorm(y: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: torch.Tensor, groups: int,
-                        gate_first: bool, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+                        gate_first: bool, eps: float, out_dtype: torch.dtype, silu_after: bool = False) -> torch.Tensor:
     """RMS norm over ``groups`` equal parts of every float32 row of ``y`` with a gate from the columns
     ``gate_col ..`` of ``gate``: ``gate_first``: ``norm(y * silu(gate)) * w``; else ``norm(y) * w *
-    sigmoid(gate)``.  Column ``c`` uses ``weight[c % len(weight)]``."""
+    sigmoid(gate)``, or, with ``silu_after``, ``norm(y) * w * silu(gate)``.  Column ``c`` uses
+    ``weight[c % len(weight)]``."""
     _chk(y, "gated_group_rmsnorm y", F32)
     T, n = y.shape
     _chk(gate, "gated_group_rmsnorm gate", F32)
@@ -1236,7 +1329,8 @@ def gated_group_rmsnorm(y: torch.Tensor, gate: torch.Tensor, gate_col: int, weig
     check(library().mi_gated_group_rmsnorm(_ptr(y), gate.data_ptr() + 4 * gate_col, gate.shape[1], _ptr(weight),
                                            _code(weight, "gated_group_rmsnorm weight"), weight.numel(), _ptr(out),
                                            _code(out, "gated_group_rmsnorm out"), T, n, int(groups),
-                                           0 if gate_first else 1, float(eps), _stream()), "gated_group_rmsnorm")
+                                           0 if gate_first else (2 if silu_after else 1), float(eps), _stream()),
+          "gated_group_rmsnorm")
     return out
 
 
@@ -1298,15 +1392,18 @@ def attention_mix_supported(nh: int, nkv: int, dk: int, dv: int, dtype: torch.dt
 def attention_mix(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, mix: Optional[torch.Tensor],
                   block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int,
                   window: int, scale: float, softcap: float, keep_first: int = 0,
-                  value_dim: int = 0, sink: bool = False) -> torch.Tensor:
+                  value_dim: int = 0, sink: bool = False, head_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a ragged batch over the paged cache with ``score <- softcap * tanh(score / softcap)``
     (``softcap`` 0: none) and then ``score_h <- sum_g mix[h, g] score_g`` (``mix`` None: none) before the
     softmax over the visible keys: key ``j`` is visible from position ``p`` iff ``j <= p`` and (``window`` is
     0 or ``j > p - window`` or ``j < keep_first``).  With ``value_dim`` a token's value is the first
     ``value_dim`` numbers of its row of ``v_cache`` (which may be the key cache itself).  With ``sink`` the
     softmax counts one key more, of score 0 and without a value: ``p_j = exp(s_j) / (1 + sum exp(s_j))``.
+    With ``head_bias`` (float32 ``[nh]``) there is no softmax: a visible key's weight is
+    ``logistic(score + head_bias[h])`` by itself, not normalised over the keys.
     Returns ``[T, nh, dv]``."""
     _chk(q, "attention_mix q")
+    _chk(head_bias, "attention_mix head_bias", F32, (q.shape[1],))
     T, nh, dk = q.shape
     _chk(k_cache, "attention_mix k_cache", q.dtype)
     _, nkv, page_size, dk2 = k_cache.shape
@@ -1326,6 +1423,13 @@ def attention_mix(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if DEBUG_BOUNDS:
         _dbg_batch("attention_mix", q_start, kv_len, block_table, T, k_cache.shape[0], page_size, int(window),
                    int(max_q_len))
+    if head_bias is not None:
+        check(library().mi_attn_mix_form(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "attention_mix q"), _ptr(mix),
+                                         _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), B, int(max_q_len),
+                                         nh, nkv, dk, dv, page_size, max_pages, int(window), float(scale),
+                                         float(softcap), int(keep_first), vrs, int(bool(sink)), _ptr(head_bias),
+                                         _stream()), "attention_mix")
+        return out
     check(library().mi_attn_mix(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "attention_mix q"), _ptr(mix),
                                 _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), B, int(max_q_len), nh, nkv,
                                 dk, dv, page_size, max_pages, int(window), float(scale), float(softcap),
@@ -1348,7 +1452,8 @@ def attention_mix_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int,
                      window: int, scale: float, softcap: float, splits: int = 1,
                      part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                     keep_first: int = 0, value_dim: int = 0, sink: bool = False) -> torch.Tensor:
+                     keep_first: int = 0, value_dim: int = 0, sink: bool = False,
+                     head_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """:func:`attention_mix` on the tensor cores (bfloat16).  ``splits > 1`` (steps of one token per request
     only): the keys of a request are cut into ``splits`` blocks whose partial results go through the float32
     scratch ``part_o`` (``B * splits * nh * dv``) and ``part_ml`` (``B * splits * nh * 2``); with
@@ -1356,6 +1461,7 @@ def attention_mix_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     (:func:`attention_mix_tc_splits`)."""
     _chk(q, "attention_mix_tc q", BF16)
     T, nh, dk = q.shape
+    _chk(head_bias, "attention_mix_tc head_bias", F32, (nh,))
     _chk(k_cache, "attention_mix_tc k_cache", BF16, (None, None, None, dk))
     _, nkv, page_size, _ = k_cache.shape
     _chk(v_cache, "attention_mix_tc v_cache", BF16, (k_cache.shape[0], nkv, page_size, None))
@@ -1375,6 +1481,13 @@ def attention_mix_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     if DEBUG_BOUNDS:
         _dbg_batch("attention_mix_tc", q_start, kv_len, block_table, T, k_cache.shape[0], page_size, int(window),
                    int(max_q_len))
+    if head_bias is not None:
+        check(library().mi_attn_mix_tc_form(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(mix), _ptr(block_table),
+                                            _ptr(q_start), _ptr(kv_len), _ptr(out), _ptr(part_o), _ptr(part_ml), B,
+                                            int(max_q_len), nh, nkv, dk, dv, page_size, max_pages, int(window),
+                                            float(scale), float(softcap), int(splits), int(keep_first), vrs,
+                                            int(bool(sink)), _ptr(head_bias), _stream()), "attention_mix_tc")
+        return out
     check(library().mi_attn_mix_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(mix), _ptr(block_table), _ptr(q_start),
                                    _ptr(kv_len), _ptr(out), _ptr(part_o), _ptr(part_ml), B, int(max_q_len), nh, nkv, dk,
                                    dv, page_size, max_pages, int(window), float(scale), float(softcap), int(splits),

@@ -69,6 +69,12 @@ _SIGNATURES = {
     "mi_latent_store": [P, I, I, P, P, P, F, P, P, I, I, I, I, P],
     "mi_latent_query": [P, P, P, P, P, I, I, I, I, I, I, P],
     "mi_sigmoid_gate": [P, L, L, P, I, I, P, I, I, I, I, P],
+    "mi_causal_conv_residual": [P, I, P, I, P, L, P, P, P, P, I, I, I, I, I, I, P],
+    "mi_delta_scan_form": [P, I, P, I, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, I, F, P],
+    "mi_attn_mix_form": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, P, P],
+    "mi_attn_mix_tc_form": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, I, P, P],
+    "mi_group_rmsnorm": [P, P, P, I, P, I, I, I, I, F, P],
+    "mi_out_norm_add_groups": [P, P, P, P, P, P, P, I, P, I, P, I, I, I, F, F, I, P],
 }
 
 

@@ -11,6 +11,11 @@ for the output.  Without a mix the heads are independent: in bfloat16, where key
 those kernels are built for, prompt portions then take the engine's tcgen05 attention and steps of single tokens
 its split-KV kernel (both know the cap and the added key).
 
+``key_weights`` ``logistic``: no softmax.  Every visible key weighs in with ``logistic(score + pb[h])`` (``pb``: a
+number per head from the checkpoint) and a query's weights are not normalised over its keys.  ``output_gate``:
+the heads' outputs are multiplied element by element with ``logistic(W_g h)`` before the output projection
+(``h`` is the part's own input).
+
 Two further options.  ``sink``: the softmax counts one key more, whose score is 0 and which has no value,
 ``p_j = exp(s_j) / (1 + sum exp(s_j))``, so a query may give its weight to nothing.  ``value_blend``: the layers
 that name the same blend share the FIRST such layer's values of a token: every later one caches and attends over
@@ -41,16 +46,21 @@ class HeadMixAttention(Mixer):
     ``pairing`` says which dimensions turn together), ``sink`` (the softmax's denominator counts one more key of
     score 0), ``value_blend`` (``{"name": ..., "first": bool, "tensor": "vmix", "declared": bool}``: the
     layers of one ``name`` blend their values with those of the layer marked ``first``; ``declared`` says
-    whether the checkpoint holds this layer's weight, which the first layer never reads), optional
-    tensor names ``q``, ``k``, ``v``, ``o``, ``mix``, ``q_norm``, ``k_norm`` below the prefix.
+    whether the checkpoint holds this layer's weight, which the first layer never reads), ``key_weights``
+    (``softmax``, default, or ``logistic``: a key's weight is ``logistic(score + head_bias[h])``, not normalised;
+    without head mix, cap and ``sink``), ``output_gate`` (the layer has a ``[heads*value_dim, hidden]`` matrix
+    whose product with the part's input, through the logistic function, multiplies the heads' outputs), optional
+    tensor names ``q``, ``k``, ``v``, ``o``, ``mix``, ``q_norm``, ``k_norm``, ``head_bias`` (default ``pb``),
+    ``gate`` (default ``g``) below the prefix.
 
     Tensors: ``<prefix>q [heads*head_dim, hidden]``, ``<prefix>k [kv_heads*head_dim, hidden]``,
     ``<prefix>v [kv_heads*value_dim, hidden]``, ``<prefix>o [hidden, heads*value_dim]``,
     ``<prefix>talk [heads, heads]`` if ``head_mix``, ``<prefix>q.norm``, ``<prefix>k.norm [head_dim]`` if
-    ``qk_norm``, ``<prefix>vmix []`` if ``value_blend``."""
+    ``qk_norm``, ``<prefix>vmix []`` if ``value_blend``, ``<prefix>pb [heads]`` with logistic key weights,
+    ``<prefix>g [heads*value_dim, hidden]`` if ``output_gate``."""
 
     graph_safe = True
-    kernel_files = ("attention_mix.cu", "attention_mix_tc.cu", "attention_prefill_tc.cu")
+    kernel_files = ("attention_mix.cu", "attention_mix_tc.cu", "attention_prefill_tc.cu", "attention_latent.cu")
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -67,7 +77,14 @@ class HeadMixAttention(Mixer):
         self.softcap = float(p.get("softcap", 0.0) or 0.0)
         self.head_mix = bool(p.get("head_mix", False))
         self.sink = bool(p.get("sink", False))
-        if not self.head_mix and self.dk == self.dv:
+        self.key_weights = p.get("key_weights", "softmax")
+        if self.key_weights not in ("softmax", "logistic"):
+            raise ValueError(f"attention: key weights '{self.key_weights}' are not 'softmax' or 'logistic'")
+        self.logistic = self.key_weights == "logistic"
+        if self.logistic and (self.head_mix or self.sink or self.softcap > 0.0):
+            raise ValueError("attention: logistic key weights go without head mix, cap and added key")
+        self.output_gate = bool(p.get("output_gate", False))
+        if not self.head_mix and self.dk == self.dv and not self.logistic:
             # independent heads of one size may decode on the engine's split-KV kernel
             self.kernel_files = type(self).kernel_files + ("attention.cu",)
         self.blend = dict(p["value_blend"]) if p.get("value_blend") else None
@@ -81,7 +98,8 @@ class HeadMixAttention(Mixer):
         if self.nkv < 1 or self.nh % self.nkv:
             raise ValueError(f"attention: {self.nh} heads are not a multiple of {self.nkv} key/value heads")
         self.names = {k: prefix + p.get(k, d) for k, d in (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"), ("mix", "talk"),
-                                                            ("q_norm", "q.norm"), ("k_norm", "k.norm"))}
+                                                            ("q_norm", "q.norm"), ("k_norm", "k.norm"),
+                                                            ("head_bias", "pb"), ("gate", "g"))}
 
     def tensor_decls(self) -> List[TensorDecl]:
         n = self.names
@@ -93,6 +111,10 @@ class HeadMixAttention(Mixer):
             out += [TensorDecl(n["q_norm"], (self.dk,), "norm"), TensorDecl(n["k_norm"], (self.dk,), "norm")]
         if self.blend is not None and self.blend_declared:
             out.append(TensorDecl(self.blend_tensor, (), "blend"))
+        if self.logistic:
+            out.append(TensorDecl(n["head_bias"], (self.nh,), "bias"))
+        if self.output_gate:
+            out.append(TensorDecl(n["gate"], (self.nh * self.dv, self.H)))
         out.append(TensorDecl(n["o"], (self.H, self.nh * self.dv)))
         return out
 
@@ -110,6 +132,9 @@ class HeadMixAttention(Mixer):
             self.q_gain = tensors[n["q_norm"]].to(device=dev, dtype=torch.float32).contiguous()
             self.k_gain = tensors[n["k_norm"]].to(device=dev, dtype=torch.float32).contiguous()
             self.qk_eps = float(self.qk_norm["eps"])
+        # the bias joins float scores
+        self.head_bias = tensors[n["head_bias"]].to(device=dev, dtype=torch.float32).contiguous() if self.logistic else None
+        self.w_gate = m(tensors[n["gate"]], dev) if self.output_gate else None
         self.inv_freq = self.position.table(dev)
         self.rot_dim = self.position.rot_dim if self.inv_freq is not None else 0
         self.neighbours = getattr(self.position, "pairing", "halves") == "neighbours"
@@ -127,7 +152,7 @@ class HeadMixAttention(Mixer):
         # bfloat16: scores and P.V on the tensor cores where the kernel is built for the sizes
         self._tensor_cores = rt.act == torch.bfloat16 and F.attention_mix_tc_supported(self.nh, self.nkv, self.dk, self.dv)
         # heads that exchange nothing (a cap and one key more act on a head's own scores)
-        self._independent_heads = self.mix is None and self.dk == self.dv
+        self._independent_heads = self.mix is None and self.dk == self.dv and not self.logistic
         # prompt portions on the tensor-memory attention: its blocks want whole SMs (a block arrangement that
         # runs another part beside this one asks)
         self.large_steps_fill_the_device = self._tensor_cores and self._independent_heads
@@ -179,7 +204,8 @@ class HeadMixAttention(Mixer):
         if not self._tensor_cores:
             # float32: one kernel for every step, sums in an order that the cut of the step cannot change
             a = F.attention_mix(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
-                                self.window, self.scale, self.softcap, self.keep_first, sink=self.sink)
+                                self.window, self.scale, self.softcap, self.keep_first, sink=self.sink,
+                                head_bias=self.head_bias)
         elif ctx.all_decode and self._split_decode and "attn_part_o" in ctx.scratch:
             # one or two requests alone cannot fill the device with splits of 512 keys
             split = TUNING.decode_split(ctx.num_requests, F.decode_split_size())
@@ -191,7 +217,8 @@ class HeadMixAttention(Mixer):
             splits = F.attention_mix_tc_splits(self._span(ctx.max_kv_len), self.keep_first)
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, 1, self.window,
                                    self.scale, self.softcap, splits, ctx.scratch["attn_mix_part_o"],
-                                   ctx.scratch["attn_mix_part_ml"], keep_first=self.keep_first, sink=self.sink)
+                                   ctx.scratch["attn_mix_part_ml"], keep_first=self.keep_first, sink=self.sink,
+                                   head_bias=self.head_bias)
         elif self._independent_heads and F.prefill_attention_tc_supported(self.dk, view.page_size):
             # heads that exchange nothing, keys and values of one size the tcgen05 kernel is built for: prompt
             # portions (and what decodes beside them) take the engine's tensor-memory attention
@@ -201,7 +228,9 @@ class HeadMixAttention(Mixer):
         else:
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
                                    self.window, self.scale, self.softcap, keep_first=self.keep_first,
-                                   sink=self.sink)
+                                   sink=self.sink, head_bias=self.head_bias)
+        if self.output_gate:
+            a = F.sigmoid_gate(a, False, linear(x, self.w_gate, torch.float32), 0, self.nh, self.dv)
         return linear(a.view(ctx.num_tokens, self.nh * self.dv), self.w_o, torch.float32)
 
 

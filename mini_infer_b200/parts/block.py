@@ -167,6 +167,129 @@ class OutputNormResidual(Block):
         layer.mixer.prefetch_first(ctx, caches.get("mixer"))
 
 
+class SandwichResidual(Block):
+    """A norm before and after each part: ``x <- x + s1 * NormB(mix(Conv(Norm(x))))``, then the same around the
+    feed-forward with norms, scale and convolution of its own.  ``mix`` is one mixer or two that read the same
+    input, ``a * Mixer(h) + b * MixerB(h)``; ``s`` is a vector of the width (layer scale); ``Conv`` an input part
+    of its own (``h + conv(h)``, with the state that a short convolution over time needs).
+
+    params: ``feed_forward`` (default True; False: a layer of a mixer alone), ``second_mixer`` (default False),
+    ``mixer_scale`` and ``second_mixer_scale`` (``a`` and ``b``, default 1), ``input_conv`` (default False: the
+    parts read the norms' outputs as they are), ``hidden_size`` and ``layer_scale`` (``{"mixer": name,
+    "feed_forward": name}`` of the tensors ``s1`` and ``s2`` below the prefix; absent: no scale).
+
+    Roles: ``mixer_norm``, ``mixer``, ``mixer_out_norm``; ``mixer_b`` with ``second_mixer``; ``mixer_conv`` with
+    ``input_conv``; ``feed_forward_norm``, ``feed_forward``, ``feed_forward_out_norm`` (and
+    ``feed_forward_conv``) with a feed-forward.  The norms give ``group_parameters()`` (weight, eps, groups).
+
+    The input norm writes float32 for the convolution, which rounds to the activation type; one kernel takes
+    the root mean squares of a part's output, multiplies by norm weight and layer scale (folded into one vector
+    when the weights are loaded) and adds to the float32 residual.  A feed-forward that leaves the sum of its
+    experts' rows to its consumer has it formed inside that kernel."""
+
+    graph_safe = True
+    accepts_deferred = True
+    kernel_files = ("residual_forms.cu",)
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        p = self.params
+        self.has_ff = bool(p.get("feed_forward", True))
+        self.second = bool(p.get("second_mixer", False))
+        self.conv = bool(p.get("input_conv", False))
+        self.a = float(p.get("mixer_scale", 1.0))
+        self.b = float(p.get("second_mixer_scale", 1.0))
+        self.scale_names = dict(p.get("layer_scale") or {})
+        self.roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_out_norm": "norm"}
+        if self.second:
+            self.roles["mixer_b"] = "mixer"
+        if self.conv:
+            self.roles["mixer_conv"] = "mixer"
+        if self.has_ff:
+            self.roles.update({"feed_forward_norm": "norm", "feed_forward": "feed_forward",
+                               "feed_forward_out_norm": "norm"})
+            if self.conv:
+                self.roles["feed_forward_conv"] = "mixer"
+        self._folded = {}
+        self._ab = None
+        self._ab_before = []
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        H = int(self.params["hidden_size"]) if self.scale_names else 0
+        return [TensorDecl(self.prefix + name, (H,), "norm") for part, name in sorted(self.scale_names.items())
+                if part == "mixer" or self.has_ff]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        self.scales = {part: tensors[self.prefix + name].to(device=rt.device, dtype=torch.float32).contiguous()
+                       for part, name in self.scale_names.items() if part == "mixer" or self.has_ff}
+        self._folded = {}
+
+    def _out_weight(self, part: str, norm):
+        """Weight of the output norm times the layer scale, eps, groups."""
+        got = self._folded.get(part)
+        if got is None:
+            fn = getattr(norm, "group_parameters", None)
+            if fn is not None:
+                w, eps, groups = fn()
+            else:
+                rms = norm.rms_parameters()
+                if rms is None:
+                    raise ValueError("sandwich_residual: the norm of a part's output must be an RMS norm")
+                w, eps, groups = rms[0], rms[1], 1
+            w = w.to(torch.float32)
+            if part in self.scales:
+                w = (w * self.scales[part]).contiguous()
+            got = self._folded[part] = (w, eps, groups)
+        return got
+
+    def _weights(self, T: int, device):
+        """``[T, 1]`` times ``a`` and ``[T]`` times ``b``: the two mixers' weights as the weights of a sum of rows."""
+        if self._ab is None or self._ab[0].shape[0] < T or self._ab[0].device != device:
+            # a captured pass keeps reading the tensors it was captured with: smaller ones stay alive
+            self._ab_before.append(self._ab)
+            n = max(T, 1024)
+            self._ab = (torch.full((n, 1), self.a, dtype=torch.float32, device=device),
+                        torch.full((n,), self.b, dtype=torch.float32, device=device))
+        return self._ab[0][:T], self._ab[1][:T]
+
+    def _read(self, hidden: torch.Tensor, norm, conv, ctx: StepContext, cache) -> torch.Tensor:
+        if conv is None:
+            return apply_norm(norm, hidden, None)
+        return conv.forward(norm.apply_float(hidden), ctx, cache)
+
+    def _add(self, hidden: torch.Tensor, y, part: str, norm) -> None:
+        w, eps, groups = self._out_weight(part, norm)
+        if isinstance(y, WeightedRowSum):
+            y = (y.rows, y.index, y.weights, y.extra, y.scale)
+        else:
+            y = resolve(y)
+        F.out_norm_add(hidden, y, w, eps, 1.0, None, groups=groups)
+
+    def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, caches):
+        left = resolve(pending)
+        if left is not None:
+            hidden.add_(left)
+        h = self._read(hidden, layer.mixer_norm, layer.mixer_conv if self.conv else None, ctx, caches.get("mixer_conv"))
+        y = layer.mixer.forward(h, ctx, caches.get("mixer"))
+        if self.second:
+            # a * y + b * y2 is formed inside the output norm's kernel, as a sum of rows with weights
+            y2 = layer.mixer_b.forward(h, ctx, caches.get("mixer_b"))
+            wa, wb = self._weights(y.shape[0], y.device)
+            y = WeightedRowSum(y, None, wa, y2, wb)
+        elif self.a != 1.0:
+            y = WeightedRowSum(y, None, self._weights(y.shape[0], y.device)[0], None, None)
+        self._add(hidden, y, "mixer", layer.mixer_out_norm)
+        if self.has_ff:
+            h = self._read(hidden, layer.feed_forward_norm, layer.feed_forward_conv if self.conv else None, ctx,
+                           caches.get("feed_forward_conv"))
+            self._add(hidden, layer.feed_forward.forward_deferred(h, ctx), "feed_forward", layer.feed_forward_out_norm)
+        return None
+
+    def prefetch_layer(self, layer: BuiltLayer, ctx: StepContext, caches) -> None:
+        layer.mixer.prefetch_first(ctx, caches.get("mixer"))
+
+
 class ParallelResidual(Block):
     """``x <- x + Mixer(Norm1(x)) + FFN(Norm2(x))``: both parts read the same residual and their outputs
     are added together.  params: ``feed_forward`` (default True; False: a layer of a mixer alone, with the
@@ -282,6 +405,7 @@ class StreamMerge(Block):
 register_part("block", "prenorm_residual", PreNormResidual)
 register_part("block", "parallel_residual", ParallelResidual)
 register_part("block", "output_norm_residual", OutputNormResidual)
+register_part("block", "sandwich_residual", SandwichResidual)
 register_part("block", "stream_merge", StreamMerge)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("lm_head", "linear", LinearHead)

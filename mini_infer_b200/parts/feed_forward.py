@@ -114,6 +114,8 @@ class SparseMoE(FeedForward):
     ``slope``, as in :class:`GatedMLP`); ``router_bias`` (the router has a bias per expert that joins the
     logits before the choice); ``scoring`` (``softmax``, default, or ``sigmoid``: every expert's score is the
     logistic function of its own logit, the largest are chosen and are the weights);
+    ``expert_groups`` (``(count, keep)``: the experts form ``count`` equal groups of neighbours, a group's score is
+    the largest score in it, and only experts of the ``keep`` best groups can be chosen; softmax scoring);
     ``weight_input`` (the weight multiplies what the expert READS, ``sum_k expert_k(w_k x)``, instead of what
     it puts out: the gated unit is not linear, so the two differ; the first product is, so the weight is
     applied to both of its halves in the epilogue, ``act(w g) (w u)`` with ``g``, ``u`` the products of the
@@ -156,6 +158,17 @@ class SparseMoE(FeedForward):
         if self.scoring not in ("softmax", "sigmoid"):
             raise ValueError(f"moe: scoring '{self.scoring}' is not 'softmax' or 'sigmoid'")
         self.weight_input = bool(p.get("weight_input", False))
+        self.groups = None
+        if p.get("expert_groups"):
+            count, keep = (int(v) for v in p["expert_groups"])
+            if count < 1 or self.E % count or not 1 <= keep <= count:
+                raise ValueError(f"moe: {self.E} experts in {count} groups of which {keep} stay eligible")
+            if keep < count:
+                if self.scoring != "softmax":
+                    raise ValueError("moe: expert groups are built for softmax scores")
+                if self.K > keep * (self.E // count):
+                    raise ValueError(f"moe: top_k {self.K} exceeds the {keep * (self.E // count)} eligible experts")
+                self.groups = (count, keep)
         self._shared_prefix = self.prefix + p.get("shared", "shared_expert.")
         self._shared_gate_name = self.prefix + p.get("shared_gate", "shared_expert_gate.weight")
         self._ones = None
@@ -278,6 +291,7 @@ class SparseMoE(FeedForward):
             # the routing that comes first hardly touches memory: the shared expert's weights arrive beside it
             ctx.prefetch((self.w_shared_gate_up, self.w_shared_down))
         if (rms is not None and self.b_router is None and self.scoring == "softmax" and not self.weight_input
+                and self.groups is None
                 and T <= TUNING.shared_expert_fork_after_routing_max_tokens and self._by_pair(T)
                 and F.norm_route_small_takes(self.H, self.E, self.w_shared_gate is not None, self.w_router.dtype)
                 and (delta is None or isinstance(delta, torch.Tensor))):
@@ -333,7 +347,8 @@ class SparseMoE(FeedForward):
             else:
                 idx, w, gate, probs, _, _, _ = F.moe_route_small(
                     x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
-                    want_probs=self.keep_routing, permute=False, bias=self.b_router, scoring=self.scoring)
+                    want_probs=self.keep_routing, permute=False, bias=self.b_router, scoring=self.scoring,
+                    groups=self.groups)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
             # (weights on the experts' inputs: result rows are indexed by pair, as the weights are)
@@ -352,11 +367,11 @@ class SparseMoE(FeedForward):
                     and self.rt.act == torch.bfloat16:
                 idx, w, gate, probs, offsets, sorted_token, inv_perm = F.moe_route_small(
                     x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
-                    want_probs=self.keep_routing, bias=self.b_router, scoring=self.scoring)
+                    want_probs=self.keep_routing, bias=self.b_router, scoring=self.scoring, groups=self.groups)
             else:
                 idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
                                                    want_probs=self.keep_routing, bias=self.b_router,
-                                                   scoring=self.scoring)
+                                                   scoring=self.scoring, groups=self.groups)
                 offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)

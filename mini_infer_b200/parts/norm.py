@@ -83,5 +83,60 @@ class ScalarRMSNorm(Norm):
         return F.add2_rmsnorm_scalar(hidden, a, b, self.scalar_gain, other.scalar_gain, self.eps, self.rt.act)
 
 
+class GroupedRMSNorm(Norm):
+    """RMS norm in groups: a row is split into ``groups`` equal consecutive parts, each is divided by its own
+    ``sqrt(mean(part^2) + eps)``, and the whole is multiplied by the weight.  params: ``size``, ``eps``,
+    ``groups`` (default 1), optional ``tensor`` (the tensor's name below the prefix, default ``weight``).
+    Tensor: ``<prefix><tensor> [size]``.
+
+    ``apply_float`` returns the normalised rows unrounded, for an arrangement whose next step (a short
+    convolution, say) still works in float32; ``group_parameters()`` hands ``(weight, eps, groups)`` to a block
+    that runs the norm inside a kernel of its own."""
+
+    graph_safe = True
+    kernel_files = ("residual_forms.cu",)
+
+    def _name(self) -> str:
+        return self.prefix + self.params.get("tensor", "weight")
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        return [TensorDecl(self._name(), (self.params["size"],), "norm")]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        self.eps = float(self.params["eps"])
+        self.groups = int(self.params.get("groups", 1))
+        if self.groups < 1 or int(self.params["size"]) % self.groups:
+            raise ValueError(f"rmsnorm_grouped: {self.params['size']} columns do not split into {self.groups} groups")
+        # the norm is float arithmetic
+        self.weight = tensors[self._name()].to(device=rt.device, dtype=torch.float32).contiguous()
+
+    def group_parameters(self):
+        return self.weight, self.eps, self.groups
+
+    def rms_parameters(self):
+        return (self.weight, self.eps) if self.groups == 1 else None
+
+    def _updated(self, hidden: torch.Tensor, delta) -> torch.Tensor:
+        if isinstance(delta, Deferred):
+            delta = delta.materialize()
+        if delta is not None:
+            hidden.add_(delta)
+        return hidden
+
+    def apply(self, hidden: torch.Tensor, delta, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if rows is not None and delta is not None:
+            # the last norm of a model: only the wanted rows are read, the residual is left as it is
+            d = delta.materialize() if isinstance(delta, Deferred) else delta
+            if d is not None:
+                hidden = hidden + d
+            delta = None
+        return F.group_rmsnorm(self._updated(hidden, delta), self.weight, self.groups, self.eps, self.rt.act, rows)
+
+    def apply_float(self, hidden: torch.Tensor, delta=None) -> torch.Tensor:
+        return F.group_rmsnorm(self._updated(hidden, delta), self.weight, self.groups, self.eps, torch.float32)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "rmsnorm_grouped", GroupedRMSNorm)
 register_part("norm", "rmsnorm_scalar", ScalarRMSNorm)
