@@ -1,8 +1,8 @@
 """A plain, slow Bogetar: one function per mechanism, float64 on the CPU, written from the design's
 equations and sharing no code with the engine.
 
-``forward(config, weights, tokens)`` runs one whole sequence and returns ``(logits [T, V], residual stream
-after every layer [L, T, W])``.  ``weights`` maps checkpoint names to tensors.  With ``rnd`` (a function that
+``forward(config, weights, tokens)`` runs one whole sequence and returns the logits ``[T, V]`` (with
+``layers_out``, a list, the residual stream after every layer is appended to it).  ``weights`` maps checkpoint names to tensors.  With ``rnd`` (a function that
 rounds a tensor, ``as_bfloat16``) the places where the engine's bfloat16 path stores 16 bits are rounded too,
 so that a tiny model's own sensitivity to rounding does not drown a comparison.  ``forced`` replays expert
 choices (``{layer: [T, top] indices}``) after a test has checked that they are legitimate.
@@ -19,10 +19,10 @@ F64 = torch.float64
 
 
 def as_bfloat16(x: torch.Tensor) -> torch.Tensor:
-    return x.to(torch.bfloat16).to(F64)
+    return x.to(torch.bfloat16).to(x.dtype)
 
 
-def _same(x: torch.Tensor) -> torch.Tensor:
+def same(x: torch.Tensor) -> torch.Tensor:
     return x
 
 
@@ -62,8 +62,8 @@ def rotate_halves(x: torch.Tensor, positions: torch.Tensor, dims: int, base: flo
     if dims == 0:
         return x
     half = dims // 2
-    freq = torch.tensor([base ** (-2.0 * i / dims) for i in range(half)], dtype=F64)
-    ang = positions.to(F64)[:, None] * freq[None, :]
+    freq = torch.tensor([base ** (-2.0 * i / dims) for i in range(half)], dtype=x.dtype)
+    ang = positions.to(x.dtype)[:, None] * freq[None, :]
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     u, v = x[..., :half], x[..., half:dims]
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
@@ -87,11 +87,11 @@ def windowed_sigmoid_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: s
     v = rnd(v)
     i, j = pos[:, None], pos[None, :]
     visible = (j <= i) & (i - j < m["mask"]["size"])
-    out = torch.zeros(T, H, dv, dtype=F64)
+    out = torch.zeros(T, H, dv, dtype=h.dtype)
     for hd in range(H):
         g = hd // (H // G)
         score = (q[:, hd] @ k[:, g].T) * m["scale"] + W[p + "pb"][hd]
-        weight = torch.where(visible, sigmoid(score), torch.zeros((), dtype=F64))
+        weight = torch.where(visible, sigmoid(score), torch.zeros((), dtype=h.dtype))
         out[:, hd] = weight @ v[:, g]
     gate = sigmoid(h @ W[p + "g"].T)
     return rnd(rnd(out.reshape(T, H * dv)) * gate) @ W[p + "o"].T
@@ -107,8 +107,8 @@ def gated_linear_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, 
     v = (h @ W[p + "v"].T).reshape(T, H, dv)
     z = rnd(h @ W[p + "a1"].T) @ W[p + "a2"].T + W[p + "a2.b"]
     alpha = (sigmoid(z) ** (1.0 / m["tau"])).reshape(T, H, d)
-    S = torch.zeros(H, d, dv, dtype=F64)
-    o = torch.zeros(T, H, dv, dtype=F64)
+    S = torch.zeros(H, d, dv, dtype=h.dtype)
+    o = torch.zeros(T, H, dv, dtype=h.dtype)
     for t in range(T):
         S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
         o[t] = torch.einsum("hkv,hk->hv", S, q[t])
@@ -135,8 +135,8 @@ def gated_delta_rule(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dic
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = sigmoid(h @ W[p + "b"].T)
     g = torch.exp(-torch.exp(W[p + "A_log"]) * softplus(h @ W[p + "a"].T + W[p + "dt_bias"]))
-    S = torch.zeros(H, d, dv, dtype=F64)
-    o = torch.zeros(T, H, dv, dtype=F64)
+    S = torch.zeros(H, d, dv, dtype=h.dtype)
+    o = torch.zeros(T, H, dv, dtype=h.dtype)
     rep = H // G
     for t in range(T):
         kt = k[t].repeat_interleave(rep, dim=0)
@@ -178,7 +178,7 @@ def mixture_of_experts(h, W, p, mlp, rnd, forced=None):
     idx, s = route(h, W[p + "router"], r)
     if forced is not None:
         idx = forced
-    out = torch.zeros(h.shape[0], W[p + "e0.down"].shape[0], dtype=F64)
+    out = torch.zeros(h.shape[0], W[p + "e0.down"].shape[0], dtype=h.dtype)
     for e in range(r["experts"]):
         rows = (idx == e).any(dim=-1).nonzero().flatten()
         if rows.numel():
@@ -187,15 +187,17 @@ def mixture_of_experts(h, W, p, mlp, rnd, forced=None):
 
 
 def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, rnd: Optional[Callable] = None,
-            forced: Optional[Dict[int, torch.Tensor]] = None, routing_out: Optional[dict] = None):
-    rnd = rnd or _same
-    W = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in weights.items()}
+            forced: Optional[Dict[int, torch.Tensor]] = None, chosen: Optional[dict] = None,
+            layers_out: Optional[list] = None, dtype: torch.dtype = F64) -> torch.Tensor:
+    """``dtype`` float32 runs the same plain arithmetic in 32 bits: how far it lies from the float64 run says how
+    much rounding alone moves a position of THIS model (tiny heads make some positions ill-conditioned)."""
+    rnd = rnd or same
+    W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps, groups = config["norm"]["eps"], config["norm"].get("groups", 1)
     x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
-    after = []
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
-        h = rnd(group_rms_norm(x, W[p + "norm1"], groups, eps))
+        h = group_rms_norm(x, W[p + "norm1"], groups, eps)
         h = rnd(h + causal_conv(h, W[p + "canon1"]))
         if layer["type"] == "delta":
             y = gated_delta_rule(h, W, p + "mix.", layer["mixer"], eps, rnd)
@@ -205,13 +207,23 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, rnd: Optiona
             raise ValueError(layer["type"])
         x = x + group_rms_norm(y, W[p + "norm1b"], groups, eps) * W[p + "ls1"]
         if layer.get("mlp") is not None:
-            h = rnd(group_rms_norm(x, W[p + "norm2"], groups, eps))
+            h = group_rms_norm(x, W[p + "norm2"], groups, eps)
             h = rnd(h + causal_conv(h, W[p + "canon2"]))
             y, idx, s = mixture_of_experts(h, W, p + "mlp.", layer["mlp"], rnd,
                                            None if forced is None else forced.get(i))
-            if routing_out is not None:
-                routing_out[i] = (idx, s)
+            if chosen is not None:
+                chosen[i] = (idx, s)
             x = x + group_rms_norm(y, W[p + "norm2b"], groups, eps) * W[p + "ls2"]
-        after.append(x.clone())
+        if layers_out is not None:
+            layers_out.append(x.clone())
     h = rnd(group_rms_norm(x, W["final.norm"], groups, eps))
-    return h @ W["embed"].T, torch.stack(after)
+    return h @ W["embed"].T
+
+
+def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt, n: int):
+    ids, out = list(prompt), []
+    for _ in range(n):
+        tok = int(torch.argmax(forward(config, weights, ids)[-1]))
+        ids.append(tok)
+        out.append(tok)
+    return out
