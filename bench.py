@@ -868,6 +868,120 @@ def run_tofinex(args):
                        _tofinex_kernel_work, _tofinex_twin_kernel_work, "moe_twin", graph_prompts=True)
 
 
+# --------------------------------------------------------------------------- #
+# --bogetar: the Bogetar design beside the closest built-in model (Qwen2-MoE) at equal sizes
+# --------------------------------------------------------------------------- #
+BOGETAR_SIZES = {   # width, attention heads, key/value heads, head size, linear-attention heads, key size, value size,
+                    # delta heads, delta key heads, experts, experts per token, expert width, expert groups (count, keep)
+    "0.5b": (1024, 8, 2, 128, 8, 64, 128, 8, 4, 16, 2, 1024, (4, 2)),
+    "a2.7b": (2048, 16, 4, 128, 16, 64, 128, 16, 8, 60, 4, 1408, (6, 3)),    # the expert sizes of Qwen1.5-MoE-A2.7B
+}
+BOGETAR_LAYERS = ("parallel", "delta", "parallel", "parallel", "delta", "parallel")
+
+
+def bogetar_config(size, window, vocab):
+    W, H, G, d, RH, rd, re, DH, DG, E, K, eff, groups = BOGETAR_SIZES[size]
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0},
+           "router": {"experts": E, "top": K, "groups": {"count": groups[0], "keep": groups[1]}}}
+    parallel = {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "mask": {"size": window},
+                         "rot": {"base": 500000.0, "dims": d // 2}, "scale": d ** -0.5},
+                "right": {"heads": RH, "dim": rd, "vdim": re, "tau": 16.0, "decay_rank": 16},
+                "left_scale": 0.6, "right_scale": 0.9}
+    delta = {"heads": DH, "kv_heads": DG, "dim": d, "vdim": d, "conv": 4}
+    layers = [{"type": t, "mixer": parallel if t == "parallel" else delta, "mlp": moe} for t in BOGETAR_LAYERS]
+    return {"architecture": "Bogetar", "vocab": vocab, "width": W, "norm": {"eps": 1e-6, "groups": 2},
+            "canon": {"taps": 4}, "layers": layers}
+
+
+def bogetar_twin_config(size, window, vocab):
+    """The closest built-in model: Qwen2-MoE with the same width, attention heads, window, experts and expert
+    width, no shared expert, as many layers (all routed)."""
+    W, H, G, d, RH, rd, re, DH, DG, E, K, eff, groups = BOGETAR_SIZES[size]
+    return dict(A27B, vocab_size=vocab, hidden_size=W, intermediate_size=eff, num_hidden_layers=len(BOGETAR_LAYERS),
+                num_attention_heads=H, num_key_value_heads=G, head_dim=d, num_experts=E, num_experts_per_tok=K,
+                moe_intermediate_size=eff, shared_expert_intermediate_size=0, mlp_only_layers=[],
+                norm_topk_prob=False, use_sliding_window=True, sliding_window=window, max_window_layers=0,
+                max_position_embeddings=1 << 20)
+
+
+def _bogetar_kernel_work(cfg, T, B, ctx, decode):
+    """Algorithmic bytes and floating-point operations of the design's own kernels for one step over all layers
+    (prefill of T tokens of one request, or a decode step of B requests at context ctx)."""
+    rows, W, taps = (B if decode else T), cfg["width"], cfg["canon"]["taps"]
+    out = {}
+
+    def add(name, by, fl):
+        a = out.setdefault(name, [0.0, 0.0])
+        a[0] += by
+        a[1] += fl
+
+    def walk(H, G, d, e, form_columns):
+        # rows in (q, k, v, and what the decays are made of), the prepared rows written and read, results out; the
+        # state read and written once per request
+        state = (B if decode else 1) * H * d * e * 4 * 2
+        add("delta_scan_kernel", rows * (H * (3 * d + 4) + H * e * 2) * 4 + state, rows * H * d * e * 6.0)
+        add("delta_prepare_kernel", rows * ((2 * G * d + form_columns) * 4 + H * (3 * d + 4) * 4), 0)
+        add("gated_group_rmsnorm_kernel", rows * H * e * (4 + 4 + 2), 0)
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "delta":
+            H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            ch = 2 * G * d + H * e
+            walk(H, G, d, e, 2 * H)
+            for name in ("causal_conv_silu_kernel", "causal_conv_silu_vec4_kernel"):
+                add(name, rows * ch * 8, rows * ch * 8.0)
+        else:
+            a, r = m["left"], m["right"]
+            H, G, d, e, win = a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["mask"]["size"]
+            keys = min(ctx, win)
+            pairs = B * keys if decode else sum(min(t + 1, win) for t in range(T))
+            by = (B * keys * G * (d + e) * 2 + B * H * (d + e) * 2) if decode else T * (H + G) * (d + e) * 2
+            for name in ("attn_mix_tc_kernel", "pt::attn_prefill_tc_kernel"):
+                add(name, by, pairs * H * (2.0 * d + 2.0 * e))
+            for name in ("rope_store_kernel", "rope_store_vec_kernel"):
+                add(name, rows * (H * d + G * (d + e)) * 6, 0)
+            add("sigmoid_gate_kernel", rows * H * e * (2 + 4 + 2), 0)
+            walk(r["heads"], r["heads"], r["dim"], r["vdim"], r["heads"] * r["dim"])
+        parts = 1 if L["mlp"] is None else 2
+        # the residual's float32 row in, the normalised float32 row out; then the filter's taps and its rounded row
+        add("group_rmsnorm_kernel", parts * rows * W * 8, 0)
+        for name in ("causal_conv_silu_kernel", "causal_conv_silu_vec4_kernel"):
+            add(name, parts * rows * W * (4 + 2), parts * rows * W * 2.0 * taps)
+        # a part's float32 output in (two mixers' outputs, or the experts' rows), the residual read and written
+        for name in ("out_norm_add_kernel", "out_norm_add_vec_kernel"):
+            add(name, parts * rows * W * (4 + 8), 0)
+            if L["type"] == "parallel":
+                add(name, rows * W * 4, 0)
+            if L["mlp"] is not None:
+                add(name, rows * W * 4 * (L["mlp"]["router"]["top"] - 1), 0)
+        if L["mlp"] is not None:
+            add("tc::gather_rows_kernel", rows * W * 2 * (1 + L["mlp"]["router"]["top"]), 0)
+    return out
+
+
+def _bogetar_twin_kernel_work(cfg, size, window, T, B, ctx, decode):
+    W, H, G, d = BOGETAR_SIZES[size][:4]
+    K = BOGETAR_SIZES[size][10]
+    rows, layers = (B if decode else T), len(BOGETAR_LAYERS)
+    if decode:
+        keys = min(ctx, window)
+        pairs, by = B * keys, B * keys * G * 2 * d * 2 + B * H * 2 * d * 2
+        attn = "attn_decode_split_kernel"
+    else:
+        pairs = sum(min(t + 1, window) for t in range(T))
+        by, attn = T * (H + G) * 2 * d * 2, "pt::attn_prefill_tc_kernel"
+    return {attn: [layers * by, layers * pairs * H * 4.0 * d],
+            "qkv_post_rows_kernel": [layers * rows * (H + 2 * G) * d * 6, 0.0],
+            "add_rmsnorm_vec_kernel": [(layers + 1) * rows * W * (4 + 8 + 2), 0.0],
+            "combine_add_rmsnorm_vec_kernel": [layers * rows * W * (4 * (K + 1) + 8 + 2), 0.0],
+            "tc::gather_rows_kernel": [layers * rows * W * 2 * (1 + K), 0.0]}
+
+
+def run_bogetar(args):
+    return _run_design(args, "bogetar", args.bogetar, args.bogetar_window, bogetar_config, bogetar_twin_config,
+                       _bogetar_kernel_work, _bogetar_twin_kernel_work, "moe_twin", graph_prompts=True)
+
+
 def run_reference(args):
     """The reference arm: Deyu-Kong/mini-infer itself, unmodified, built out of tree for sm_100 by
     ``baseline/build_reference.py`` and driven by ``baseline/reference_bench.cpp`` through its stock path
@@ -1008,6 +1122,10 @@ def main():
                     help="instead of the default workload: prefill and decode of the Tofinex design beside Qwen2-MoE at "
                          "these sizes (comma-separated, of " + ", ".join(TOFINEX_SIZES) + "), see run_tofinex")
     ap.add_argument("--nipapel-window", type=int, default=1024, help="attention window of the --nipapel models")
+    ap.add_argument("--bogetar", default="", metavar="SIZES",
+                    help="instead of the default workload: the Bogetar design beside Qwen2-MoE at "
+                         "these sizes (comma-separated, of " + ", ".join(BOGETAR_SIZES) + "), see run_bogetar")
+    ap.add_argument("--bogetar-window", type=int, default=1024, help="attention window of the --bogetar models")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference's program may take")
     ap.add_argument("--reference-prefill-batch", type=int, default=1,
                     help="prompts the reference's scheduler prefills per iteration (its cuBLAS handles, one per "
@@ -1031,6 +1149,8 @@ def main():
         return run_nipapel(args)
     if args.tofinex:
         return run_tofinex(args)
+    if args.bogetar:
+        return run_bogetar(args)
     return run_ours(args)
 
 

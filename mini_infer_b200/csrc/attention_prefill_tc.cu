@@ -86,17 +86,19 @@ struct Maps {
 // scale / cap, `cap_out` = cap / scale, so that what follows scales the capped number as it scales a plain one).
 // `sink`: the softmax counts one key more, of score 0 and without a value: the reference of the exponentials
 // starts at 0 and the running sum at 1.
+// LOGISTIC: no softmax.  A visible key's weight is logistic(score * scale + head_bias[h]) by itself, not normalised
+// over the keys: nothing follows a maximum, O is never rescaled and leaves as it is.
 __device__ __forceinline__ float fast_tanh(float x) {
     return 1.0f - __fdividef(2.0f, fast_exp2(x * 2.8853900817779268f) + 1.0f);
 }
 
-template <int DK, int DV, bool CAPPED = false>
+template <int DK, int DV, bool CAPPED = false, bool LOGISTIC = false>
 __global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict__ block_table,
                        const int* __restrict__ q_start, const int* __restrict__ kv_len,
                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_pages,
                        int window, float scale_log2, int* __restrict__ status, int keep_first, int hpq,
-                       float cap_in, float cap_out, int sink) {
+                       float cap_in, float cap_out, int sink, const float* __restrict__ head_bias) {
     constexpr int DKH = DK / 64, DVH = DV / 64;           // 64-column halves of a key and of a value row
     constexpr uint32_t TMEM_COLS = 256;                   // S[0], S[1] (BN columns each), O (D): two blocks share an SM
     constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
@@ -292,6 +294,23 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             // sink_end (such a tile lies below every window, so it is always masked key by key), of a window's
             // tile those below keep_first
             const int keep_lim = j < n_sink ? sink_end : keep_first;
+            uint32_t pk[BN / 2];
+            float alpha = 1.f;
+            if constexpr (LOGISTIC) {
+                // logistic(x) = 1 / (1 + 2^(-x log2 e)); the exponent is bounded so that the power stays finite
+                const float hb = head_bias[h] * 1.4426950408889634f;
+#pragma unroll
+                for (int i = 0; i < BN; i += 2) {
+                    float w0 = __fdividef(1.0f, 1.0f + fast_exp2(fminf(-fmaf(__uint_as_float(v[i]), scale_log2, hb), 80.f)));
+                    float w1 = __fdividef(1.0f, 1.0f + fast_exp2(fminf(-fmaf(__uint_as_float(v[i + 1]), scale_log2, hb), 80.f)));
+                    if (masked) {
+                        const int kj = k0 + i;
+                        if (kj > vis_hi || (kj < vis_lo && kj >= keep_lim)) w0 = 0.f;
+                        if (kj + 1 > vis_hi || (kj + 1 < vis_lo && kj + 1 >= keep_lim)) w1 = 0.f;
+                    }
+                    pk[i >> 1] = pack_bf16(w0, w1);
+                }
+            } else {
             float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of BN steps
             if (masked) {
 #pragma unroll
@@ -315,7 +334,6 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             }
             const float base = m_ref == -INFINITY ? 0.f : m_ref;
             float sums[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pk[BN / 2];
 #pragma unroll
             for (int i = 0; i < BN; i += 2) {
                 const float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), scale_log2, -base));
@@ -324,8 +342,9 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 pk[i >> 1] = pack_bf16(e0, e1);
             }
             l_run = l_run * alpha + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+            }
             // O is scaled only after the O += P V of tile j - 1 is complete
-            const bool rescale = j > 0 && !__all_sync(0xffffffffu, alpha == 1.f);
+            const bool rescale = !LOGISTIC && j > 0 && !__all_sync(0xffffffffu, alpha == 1.f);
             if (rescale) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, 18);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -363,7 +382,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
         }
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const float inv = LOGISTIC ? 1.f : (l_run > 0.f ? 1.f / l_run : 0.f);
             __nv_bfloat16* dst = out + ((int64_t)(q0 + qt * BQ + r) * nh + h) * DV;
 #pragma unroll 1
             for (int c0 = 0; c0 < DV; c0 += 32) {
@@ -471,11 +490,63 @@ int mi_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
         kern<<<grid, 192, smem, stream>>>(maps, block_table, q_start, kv_len, (__nv_bfloat16*)out, nh,    \
                                           nkv, page_size, max_pages, window, scale_log2, status,          \
-                                          keep_first, 1, cap_in, cap_out, sink);                          \
+                                          keep_first, 1, cap_in, cap_out, sink, nullptr);                 \
     } while (0)
     if (cap > 0.f) { if (d == 64) MI_PT(64, true); else MI_PT(128, true); }
     else { if (d == 64) MI_PT(64, false); else MI_PT(128, false); }
 #undef MI_PT
+    return finish_launch("attn_prefill_tc");
+}
+
+// The same kernel with logistic key weights that are not normalised (see LOGISTIC above): key and value heads of
+// 64 or 128 numbers each, not necessarily alike; q [T, nh, dk], out [T, nh, dv]; head_bias float [nh].
+int mi_attn_prefill_tc_logistic_supported(int dk, int dv, int page_size) {
+    return (dk == 64 || dk == 128) && (dv == 64 || dv == 128) && mi_attn_prefill_tc_supported(64, page_size);
+}
+
+int mi_attn_prefill_tc_logistic(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                const int* q_start, const int* kv_len, void* out, int* status, int T, int B,
+                                int max_q_len, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
+                                int max_pages, int window, float scale, const float* head_bias, cudaStream_t stream) {
+    if (B <= 0 || max_q_len <= 0 || T <= 0) return kOk;
+    if (!mi_attn_prefill_tc_logistic_supported(dk, dv, page_size) || !head_bias || !(scale > 0.f)) {
+        set_last_error("prefill attention with logistic weights (tcgen05): keys of %d, values of %d, pages of %d tokens "
+                       "are not taken, or the heads' biases are missing", dk, dv, page_size);
+        return kBadShape;
+    }
+    if (nkv < 1 || nh % nkv != 0 || B > 65535 || nh > 65535) {
+        set_last_error("attention: %d query heads over %d key/value heads, batch %d", nh, nkv, B);
+        return kBadShape;
+    }
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+         reinterpret_cast<uintptr_t>(out)) & 15) {
+        set_last_error("prefill attention (tcgen05): operands must be 16-byte aligned");
+        return kBadShape;
+    }
+    pt::Maps maps;
+    const uint64_t cache_rows = (uint64_t)num_pages * nkv * page_size;
+    bool ok = pt::make_map_pitched(&maps.q, q, (uint64_t)T, (uint64_t)nh * dk, (uint64_t)nh * dk, pt::BQ) &&
+              pt::make_map_pitched(&maps.k, k_cache, cache_rows, (uint64_t)dk, (uint64_t)dk, (uint32_t)page_size) &&
+              pt::make_map_pitched(&maps.v, v_cache, cache_rows, (uint64_t)dv, (uint64_t)dv, (uint32_t)page_size);
+    if (!ok) {
+        set_last_error("prefill attention (tcgen05): cuTensorMapEncodeTiled failed");
+        return kLaunchFailed;
+    }
+    const dim3 grid((max_q_len + pt::BQ - 1) / pt::BQ, nh, B);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const size_t smem = (size_t)(dk / 64) * pt::HALF_BYTES +
+                        (size_t)(pt::NK * (dk / 64) + pt::NV * (dv / 64)) * pt::KV_HALF + 256;
+#define MI_PTL(KK, VV)                                                                                    \
+    do {                                                                                                  \
+        auto kern = pt::attn_prefill_tc_kernel<KK, VV, false, true>;                                      \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
+        kern<<<grid, 192, smem, stream>>>(maps, block_table, q_start, kv_len, (__nv_bfloat16*)out, nh,    \
+                                          nkv, page_size, max_pages, window, scale_log2, status, 0, 1,    \
+                                          0.f, 0.f, 0, head_bias);                                        \
+    } while (0)
+    if (dk == 64) { if (dv == 64) MI_PTL(64, 64); else MI_PTL(64, 128); }
+    else { if (dv == 64) MI_PTL(128, 64); else MI_PTL(128, 128); }
+#undef MI_PTL
     return finish_launch("attn_prefill_tc");
 }
 
@@ -524,7 +595,7 @@ int mi_attn_prefill_tc_shared(const void* q, const void* cache, const int* block
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
         kern<<<grid, 192, smem, stream>>>(maps, block_table, q_start, kv_len, (__nv_bfloat16*)out, 1, 1,  \
                                           page_size, max_pages, window, scale_log2, status, keep_first, H,  \
-                                          0.f, 0.f, 0);                                                     \
+                                          0.f, 0.f, 0, nullptr);                                            \
     } while (0)
     if (dv == 64) {
         if (DKr == 64) MI_PTS(64, 64); else if (DKr == 128) MI_PTS(128, 64); else if (DKr == 192) MI_PTS(192, 64); else MI_PTS(256, 64);

@@ -391,6 +391,45 @@ def prefill_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     return out
 
 
+def prefill_attention_tc_logistic_supported(dk: int, dv: int, page_size: int) -> bool:
+    return bool(library().mi_attn_prefill_tc_logistic_supported(int(dk), int(dv), int(page_size)))
+
+
+def prefill_attention_tc_logistic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                  block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor,
+                                  max_q_len: int, window: int, scale: float, head_bias: torch.Tensor) -> torch.Tensor:
+    """The tcgen05 attention without a softmax: a visible key's weight is ``logistic(score * scale +
+    head_bias[h])`` by itself, not normalised over the keys (the contract of :func:`attention_mix` with
+    ``head_bias``).  bfloat16; key and value heads of 64 or 128 numbers each, not necessarily alike.  Returns
+    ``[T, nh, dv]``.  Call :func:`check_tc_status` after the step."""
+    global _tc_pending
+    _chk(q, "prefill_attention_tc_logistic q", BF16)
+    T, nh, dk = q.shape
+    _chk(k_cache, "prefill_attention_tc_logistic k_cache", BF16, (None, None, None, dk))
+    num_pages, nkv, page_size, _ = k_cache.shape
+    _chk(v_cache, "prefill_attention_tc_logistic v_cache", BF16, (num_pages, nkv, page_size, None))
+    dv = v_cache.shape[3]
+    _chk(head_bias, "prefill_attention_tc_logistic head_bias", F32, (nh,))
+    _chk(block_table, "prefill_attention_tc_logistic block_table", I32)
+    B, max_pages = block_table.shape
+    _chk(q_start, "prefill_attention_tc_logistic q_start", I32, (B + 1,))
+    _chk(kv_len, "prefill_attention_tc_logistic kv_len", I32, (B,))
+    out = torch.empty(T, nh, dv, dtype=BF16, device=q.device)
+    dev = q.device
+    if dev not in _tc_status:
+        _tc_status[dev] = torch.zeros(1, dtype=I32, device=dev)
+    if DEBUG_BOUNDS:
+        _dbg_batch("prefill_attention_tc_logistic", q_start, kv_len, block_table, T, num_pages, page_size, int(window),
+                   int(max_q_len))
+    check(library().mi_attn_prefill_tc_logistic(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(q_start),
+                                                _ptr(kv_len), _ptr(out), _ptr(_tc_status[dev]), T, B, int(max_q_len),
+                                                nh, nkv, dk, dv, page_size, num_pages, max_pages, int(window),
+                                                float(scale), _ptr(head_bias), _stream()),
+          "prefill_attention_tc_logistic")
+    _tc_pending = True
+    return out
+
+
 def prefill_attention_tc_shared_supported(heads: int, dk: int, dv: int, page_size: int) -> bool:
     return bool(library().mi_attn_prefill_tc_shared_supported(int(heads), int(dk), int(dv), int(page_size)))
 

@@ -73,6 +73,7 @@ _SIGNATURES = {
     "mi_delta_scan_form": [P, I, P, I, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, I, F, P],
     "mi_attn_mix_form": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, P, P],
     "mi_attn_mix_tc_form": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, I, P, P],
+    "mi_attn_prefill_tc_logistic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "mi_group_rmsnorm": [P, P, P, I, P, I, I, I, I, F, P],
     "mi_out_norm_add_groups": [P, P, P, P, P, P, P, I, P, I, P, I, I, I, F, F, I, P],
 }
@@ -100,6 +101,7 @@ _OTHERS = {
     "mi_attn_mix_tc_splits": ([I], c_int),
     "mi_attn_mix_supported": ([I, I, I, I, I], c_int),
     "mi_attn_prefill_tc_shared_supported": ([I, I, I, I], c_int),
+    "mi_attn_prefill_tc_logistic_supported": ([I, I, I], c_int),
     "mi_attn_decode_split_size": ([], c_int),
 }
 

@@ -156,6 +156,10 @@ class HeadMixAttention(Mixer):
         # prompt portions on the tensor-memory attention: its blocks want whole SMs (a block arrangement that
         # runs another part beside this one asks)
         self.large_steps_fill_the_device = self._tensor_cores and self._independent_heads
+        # logistic key weights on the tensor-memory attention: key and value heads of 64 or 128 numbers
+        self._logistic_tc = (self.logistic and rt.act == torch.bfloat16 and self.keep_first == 0
+                             and self.dk in (64, 128) and self.dv in (64, 128))
+        self.large_steps_fill_the_device = self.large_steps_fill_the_device or self._logistic_tc
         # single tokens of independent heads in bfloat16: the engine's split-KV kernel where it is built for
         # the head size (it reads keys and values once per head at the memory's speed and keeps no first keys)
         self._split_decode = (rt.act == torch.bfloat16 and self._independent_heads and self.keep_first == 0
@@ -219,6 +223,10 @@ class HeadMixAttention(Mixer):
                                    self.scale, self.softcap, splits, ctx.scratch["attn_mix_part_o"],
                                    ctx.scratch["attn_mix_part_ml"], keep_first=self.keep_first, sink=self.sink,
                                    head_bias=self.head_bias)
+        elif self._logistic_tc and F.prefill_attention_tc_logistic_supported(self.dk, self.dv, view.page_size):
+            # prompt portions (and what decodes beside them) with logistic weights on the tensor-memory attention
+            a = F.prefill_attention_tc_logistic(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
+                                                self.window, self.scale, self.head_bias)
         elif self._independent_heads and F.prefill_attention_tc_supported(self.dk, view.page_size):
             # heads that exchange nothing, keys and values of one size the tcgen05 kernel is built for: prompt
             # portions (and what decodes beside them) take the engine's tensor-memory attention

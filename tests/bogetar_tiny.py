@@ -95,7 +95,21 @@ CONFIG_D = {
     ],
 }
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
+# key and value heads of 64 and 128 numbers, alike and not: prompt portions in bfloat16 take the tensor-memory
+# attention, single tokens the split kernel
+CONFIG_E = {
+    "architecture": "Bogetar", "vocab": 192, "width": 128, "norm": {"eps": 1e-5, "groups": 4}, "canon": {"taps": 2},
+    "layers": [
+        _parallel(_left(6, 3, 64, 128, 50, 0.11, {"base": 10000.0, "dims": 32}), _right(2, 16, 16, 4.0, 8), 0.9, 0.6,
+                  _moe(64, 6, 2, 2.0, (3, 2))),
+        _delta(4, 2, 16, 32, 3, _moe(64, 4, 1, 1.5)),
+        _parallel(_left(2, 1, 128, 64, 200, 0.08, {"base": 5000.0, "dims": 128}), _right(4, 8, 8, 2.0, 4), 0.7, 1.1,
+                  _moe(128, 4, 2, 3.0, (2, 1))),
+        _parallel(_left(3, 3, 128, 128, 17, 0.08), _right(1, 32, 32, 32.0, 2), 1.0, 0.5, None),
+    ],
+}
+
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E}
 
 
 def make_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:

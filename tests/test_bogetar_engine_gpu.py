@@ -119,7 +119,7 @@ def run_and_check(runner, steps, cfg, w, reqs, dtype):
     return got, routing
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_every_cutting_against_the_plain_model(models, name, dtype):
     folder, cfg, w = models[name]
@@ -134,8 +134,11 @@ def test_every_cutting_against_the_plain_model(models, name, dtype):
         results.append(got)
         routings.append(routing)
         assert runner.cache.used_pages() == [0] * len(runner.cache.pools)
-    if name == "C" and dtype == "bfloat16":
+    if name in "CE" and dtype == "bfloat16":
         assert all(l.parts["mixer"]._tensor_cores for l in runner.model.layers if "mixer_b" in l.parts)
+    if name == "E" and dtype == "bfloat16":
+        # prompt portions took the tensor-memory attention
+        assert all(l.parts["mixer"]._logistic_tc for l in runner.model.layers if "mixer_b" in l.parts)
     if dtype == "float32":
         # the 32-bit path gives the same bits however the work was cut and batched
         for other, routing in zip(results[1:5], routings[1:5]):

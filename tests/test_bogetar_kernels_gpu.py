@@ -277,7 +277,10 @@ def run_attention(q, k, v, scale, bias, window, cuts, dtype=torch.float32, page_
                     table[p] = -1
         table = i32([table])
         qq = q[lo:lo + n].to(dtype).to(DEV).contiguous()
-        if tensor_cores:
+        if tensor_cores == "memory" and n > 1:
+            got = F().prefill_attention_tc_logistic(qq, kc, vc, table, i32([0, n]), i32([lo + n]), n, window, scale,
+                                                    bias.to(DEV))
+        elif tensor_cores:
             if n == 1:
                 splits = F().attention_mix_tc_splits(min(window, lo + 1))
                 po = torch.empty(splits * H * e, device=DEV)
@@ -324,14 +327,33 @@ def test_logistic_key_weights_on_the_tensor_cores(H, G, d, e, window):
         assert close(got, want, 1.5e-2), cuts
 
 
-@pytest.mark.parametrize("tensor_cores", [False, True])
+@pytest.mark.parametrize("H,G,d,e,window", [(4, 2, 64, 128, 70), (2, 1, 128, 128, 300), (6, 3, 64, 64, 5), (4, 4, 128, 64, 129),
+                                            (3, 1, 64, 128, 64)])
+@pytest.mark.parametrize("page_size", [8, 16, 64])
+def test_logistic_key_weights_on_the_tensor_memory_attention(H, G, d, e, window, page_size):
+    """Prompt portions on the tcgen05 kernel (single tokens between them on the split kernel), portions that start
+    inside key tiles and pages, with the pages behind the window given back."""
+    g = torch.Generator().manual_seed(H + d + e)
+    T = 400
+    r = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).float()
+    q, k, v = r(T, H, d), r(T, G, d), r(T, G, e)
+    bias = torch.randn(H, generator=g) - 1
+    want = plain_attention(q, k, v, 0.1, bias, window)
+    for cuts in ([T], [250, 1, 1, 148], [7, 2, 130, 3, 2, 5, 17, 2, 131, 101]):
+        got = run_attention(q, k, v, 0.1, bias, window, cuts, dtype=torch.bfloat16, tensor_cores="memory",
+                            page_size=page_size, freed_behind_window=True)
+        assert close(got, want, 1.5e-2), cuts
+    F().check_tc_status()
+
+
+@pytest.mark.parametrize("tensor_cores", [False, True, "memory"])
 @pytest.mark.parametrize("decoded", [False, True])
 @pytest.mark.parametrize("window", [1, 2, 8, 9, 63, 64, 65, 136, 257])
 def test_a_key_that_stands_out_just_inside_and_just_outside_the_window(window, decoded, tensor_cores):
     """The head's bias pushes every ordinary key's weight to nothing; one key carries a score that brings its own
     weight to one.  The last query must put out that key's value while the key is among the last ``window``
     positions, and nothing once it is one position further back."""
-    H, G, d, e = 4, 2, 16, 64
+    H, G, d, e = 4, 2, 64, 64
     dtype = torch.bfloat16 if tensor_cores else torch.float32
     g = torch.Generator().manual_seed(window)
     T = 300
