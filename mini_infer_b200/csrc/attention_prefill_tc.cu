@@ -327,7 +327,6 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * scale_log2;
             // the reference follows the maximum only when that moved by more than 8: exponentials stay
             // below 2^8, and O needs scaling only then
-            float alpha = 1.f;
             if (mx > m_ref + 8.f || (m_ref == -INFINITY && mx > -INFINITY)) {
                 alpha = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx);
                 m_ref = mx;

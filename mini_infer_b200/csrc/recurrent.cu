@@ -129,6 +129,47 @@ conv_state_update_kernel(const float* __restrict__ x, int ldx, float* __restrict
     }
 }
 
+// A step of ONE token per request: the norm in groups of the token's residual row, x + conv(x) over the request's
+// last taps-1 normalised rows (its state) and this one, the rounded row out, and the state moved on by one token,
+// in one launch (the three kernels that a step of any shape takes, for the shape that decoding repeats).  A block
+// takes `chunk` columns of one request, all inside one group of the norm, whose root mean square it forms itself
+// (blocks of one group form it alike).  w_conv float [C][taps].
+template <typename OT>
+__global__ void __launch_bounds__(128)
+norm_conv_decode_kernel(const float* __restrict__ hidden, const float* __restrict__ norm_w, int groups, float eps,
+                        const float* __restrict__ w_conv, float* __restrict__ state, int64_t state_stride,
+                        const int* __restrict__ q_start, const int* __restrict__ state_slot, OT* __restrict__ out,
+                        int C, int taps, int chunk) {
+    __shared__ float scratch[32];
+    wait_for_earlier_kernels();
+    const int b = blockIdx.x, c_lo = blockIdx.y * chunk;
+    const int64_t t = q_start[b];
+    const float* x = hidden + t * C;
+    const int gs = C / groups, g = c_lo / gs;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = x[g * gs + i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float rr = 1.0f / sqrtf(ss / (float)gs + eps);
+    float* st = state + (int64_t)state_slot[b] * state_stride;
+    for (int c = c_lo + threadIdx.x; c < c_lo + chunk; c += blockDim.x) {
+        const float n = x[c] * rr * norm_w[c];
+        float prev[kMaxTaps];
+#pragma unroll
+        for (int j = 0; j < kMaxTaps - 1; ++j) prev[j] = j + 1 < taps ? st[(int64_t)j * C + c] : 0.f;   // taps-1-j tokens back
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxTaps - 1; ++j) {
+            if (j + 1 < taps) {
+                acc += w_conv[(int64_t)c * taps + j] * prev[j];
+                if (j > 0) st[(int64_t)(j - 1) * C + c] = prev[j];       // one token on
+            }
+        }
+        acc += w_conv[(int64_t)c * taps + taps - 1] * n;
+        if (taps > 1) st[(int64_t)(taps - 2) * C + c] = n;
+        out[t * C + c] = from_float<OT>(n + acc);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // The two recurrences.  Block = 128 threads = 16 value columns x 8 lanes; lane r of a column holds, of that
 // column of S, the rows 4 (r + 8 m) .. 4 (r + 8 m) + 3 for m = 0 .. RP/4 - 1 (RP rows in all), so that the
@@ -614,6 +655,26 @@ int mi_causal_conv_residual(const float* x, int ldx, const void* w, int wdtype, 
                             int ld_out, int C, int taps, int T, int B, cudaStream_t stream) {
     return launch_causal_conv(x, ldx, w, nullptr, wdtype, state, state_stride, q_start, req_of_token, state_slot, out,
                               odtype, ld_out, C, taps, T, B, true, stream);
+}
+
+// One token per request (checked by the caller): norm in groups, x + conv(x), the state moved on, in one launch.
+int mi_norm_conv_decode(const float* hidden, const float* norm_w, int groups, float eps, const float* w_conv,
+                        float* state, int64_t state_stride, const int* q_start, const int* state_slot, void* out,
+                        int odtype, int B, int C, int taps, cudaStream_t stream) {
+    if (B <= 0 || C <= 0) return kOk;
+    if (taps < 1 || taps > kMaxTaps || groups < 1 || C % groups || groups > 1024) {
+        set_last_error("norm and convolution of a decode step: %d taps, %d columns in %d groups", taps, C, groups);
+        return kBadShape;
+    }
+    // columns per block: a power of two that divides a group (at most 128, a column a thread), else a whole group
+    const int gs = C / groups;
+    int chunk = gs;
+    for (int c = 128; c >= 32; c /= 2) if (gs % c == 0) { chunk = c; break; }
+    if (C / chunk > 65535 || B > 65535) { set_last_error("norm and convolution of a decode step: too many blocks"); return kBadShape; }
+    MI_DISPATCH_1(odtype, OT,
+        launch_dependent(norm_conv_decode_kernel<OT>, dim3(B, C / chunk), dim3(128), 0, stream, hidden,
+                         norm_w, groups, eps, w_conv, state, state_stride, q_start, state_slot, (OT*)out, C, taps, chunk));
+    return finish_launch("norm_conv_decode");
 }
 
 #define MI_SCAN_DISPATCH(rows, ...)                                                     \

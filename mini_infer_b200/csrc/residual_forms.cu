@@ -213,7 +213,7 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
         const float4* yv = reinterpret_cast<const float4*>(s.y + t * H + c0);
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
-            const int i = threadIdx.x + 256 * j;
+            const int i = threadIdx.x + blockDim.x * j;
             if (i < nv) y[j] = yv[i];
         }
     } else {
@@ -223,7 +223,7 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
             const float4* rv = reinterpret_cast<const float4*>(s.rows + r * H + c0);
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
-                const int i = threadIdx.x + 256 * j;
+                const int i = threadIdx.x + blockDim.x * j;
                 if (i < nv) axpy4(y[j], wk, rv[i]);
             }
         }
@@ -232,7 +232,7 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
             const float4* ev = reinterpret_cast<const float4*>(s.extra + t * H + c0);
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
-                const int i = threadIdx.x + 256 * j;
+                const int i = threadIdx.x + blockDim.x * j;
                 if (i < nv) axpy4(y[j], g, ev[i]);
             }
         }
@@ -243,7 +243,7 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
-        const int i = threadIdx.x + 256 * j;
+        const int i = threadIdx.x + blockDim.x * j;
         h[j] = i < nv ? hv[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         ss += y[j].x * y[j].x;
         ss += y[j].y * y[j].y;
@@ -254,7 +254,7 @@ out_norm_add_vec_kernel(float* __restrict__ hidden, RowSum s, const WT* __restri
     const float rr = 1.0f / sqrtf(ss / (float)gs + eps);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
-        const int i = threadIdx.x + 256 * j;
+        const int i = threadIdx.x + blockDim.x * j;
         if (i < nv) {
             const int c = c0 + 4 * i;
             h[j].x += mult * (y[j].x * rr * to_float(w[c]));
@@ -441,8 +441,12 @@ static int out_norm_add_groups(float* hidden, const float* y, const float* rows,
     if (gs % 4 == 0 && gs <= 8192 && (ptrs & 15) == 0) {
 #define MI_OUT_NORM_VEC(VPT)                                                                                         \
     MI_DISPATCH_2(adtype, AT, wdtype, WT,                                                                            \
-        launch_dependent(out_norm_add_vec_kernel<AT, WT, VPT>, dim3(T, groups), dim3(256), 0, stream, hidden, s,     \
+        launch_dependent(out_norm_add_vec_kernel<AT, WT, VPT>, dim3(T, groups), dim3(vthreads), 0, stream, hidden, s, \
                          (const WT*)w, (AT*)x_out, H, eps, mult, gs))
+        // a group narrower than 1024 columns takes a smaller block (with one group the block is as it always was,
+        // and with it the order of the sum of squares)
+        int vthreads = 256;
+        if (groups > 1) while (vthreads > 32 && vthreads * 2 >= gs) vthreads /= 2;
         if (gs <= 1024) { MI_OUT_NORM_VEC(1); }
         else if (gs <= 2048) { MI_OUT_NORM_VEC(2); }
         else if (gs <= 4096) { MI_OUT_NORM_VEC(4); }

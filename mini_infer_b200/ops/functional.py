@@ -1259,6 +1259,36 @@ def causal_conv_residual(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, 
     return out
 
 
+def norm_conv_decode(hidden: torch.Tensor, norm_weight: torch.Tensor, groups: int, eps: float, w: torch.Tensor,
+                     state: torch.Tensor, state_offset: int, q_start: torch.Tensor, state_slot: torch.Tensor,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """:func:`group_rmsnorm` and :func:`causal_conv_residual` of a step in which EVERY request brings exactly one
+    token, in one launch: ``n = norm(hidden)``, ``n + conv(n)`` over the request's last ``taps - 1`` normalised rows
+    and this one, the state moved on by one token.  ``norm_weight`` and ``w [C, taps]`` float32.  Returns ``[T, C]``
+    in ``out_dtype``.  (Its sums run in another order than the two kernels': the two agree within rounding.)"""
+    _chk(hidden, "norm_conv_decode hidden", F32)
+    T, C = hidden.shape
+    B = state_slot.numel()
+    if T != B:
+        raise ValueError(f"norm_conv_decode: {T} rows for {B} requests (one token each is the contract)")
+    _chk(norm_weight, "norm_conv_decode norm weight", F32, (C,))
+    _chk(w, "norm_conv_decode w", F32, (C, None))
+    taps = w.shape[1]
+    _chk(state, "norm_conv_decode state", F32)
+    if state.dim() != 2 or state_offset + (taps - 1) * C > state.shape[1] or groups < 1 or C % groups:
+        raise ValueError("norm_conv_decode: state section or groups out of range")
+    _chk(q_start, "norm_conv_decode q_start", I32, (B + 1,))
+    _chk(state_slot, "norm_conv_decode state_slot", I32, (B,))
+    if DEBUG_BOUNDS:
+        _dbg_range(state_slot, 0, state.shape[0], "norm_conv_decode state_slot")
+    out = torch.empty(T, C, dtype=out_dtype, device=hidden.device)
+    check(library().mi_norm_conv_decode(_ptr(hidden), _ptr(norm_weight), int(groups), float(eps), _ptr(w),
+                                        state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start),
+                                        _ptr(state_slot), _ptr(out), _code(out, "norm_conv_decode out"), B, C, taps,
+                                        _stream()), "norm_conv_decode")
+    return out
+
+
 DELTA_FORMS = {"channel_decay": 0, "head_decay": 1, "sigmoid_decay": 2}
 
 

@@ -70,6 +70,7 @@ _SIGNATURES = {
     "mi_latent_query": [P, P, P, P, P, I, I, I, I, I, I, P],
     "mi_sigmoid_gate": [P, L, L, P, I, I, P, I, I, I, I, P],
     "mi_causal_conv_residual": [P, I, P, I, P, L, P, P, P, P, I, I, I, I, I, I, P],
+    "mi_norm_conv_decode": [P, P, I, F, P, P, L, P, P, P, I, I, I, I, P],
     "mi_delta_scan_form": [P, I, P, I, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, I, F, P],
     "mi_attn_mix_form": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, P, P],
     "mi_attn_mix_tc_form": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, I, P, P],

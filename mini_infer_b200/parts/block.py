@@ -256,6 +256,9 @@ class SandwichResidual(Block):
     def _read(self, hidden: torch.Tensor, norm, conv, ctx: StepContext, cache) -> torch.Tensor:
         if conv is None:
             return apply_norm(norm, hidden, None)
+        fused = getattr(conv, "forward_from_residual", None)
+        if fused is not None:
+            return fused(hidden, norm, ctx, cache)          # the part may run the norm inside a kernel of its own
         return conv.forward(norm.apply_float(hidden), ctx, cache)
 
     def _add(self, hidden: torch.Tensor, y, part: str, norm) -> None:

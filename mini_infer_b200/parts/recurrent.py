@@ -366,6 +366,17 @@ class ResidualShortConv(Mixer):
         return F.causal_conv_residual(x, self.w, ctx.states[cache.group], 0, ctx.q_start, ctx.req_of_token,
                                       ctx.state_slot, self.rt.act)
 
+    def forward_from_residual(self, hidden: torch.Tensor, norm, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        """``forward(norm(hidden))``.  A decode step of the bfloat16 path (one token per request) runs the norm in
+        groups, the convolution and the state's update in one launch; the float32 path keeps one kernel per
+        mechanism for every step, so that its sums run in one order however a prompt was cut."""
+        groups = getattr(norm, "group_parameters", None)
+        if groups is not None and ctx.all_decode and self.rt.act == torch.bfloat16:
+            weight, eps, n = groups()
+            return F.norm_conv_decode(hidden, weight, n, eps, self.w, ctx.states[cache.group], 0, ctx.q_start,
+                                      ctx.state_slot, self.rt.act)
+        return self.forward(norm.apply_float(hidden), ctx, cache)
+
 
 register_part("mixer", "channel_gated_delta", ChannelGatedDelta)
 register_part("mixer", "gated_delta", GatedDelta)

@@ -112,6 +112,41 @@ def test_input_convolution_in_portions_and_batches(C, taps, dtype):
     assert bool((state[:, :3].cpu() != 0).all())                      # what lies before the section is left alone
 
 
+@pytest.mark.parametrize("C,taps,groups", [(48, 3, 3), (192, 4, 2), (40, 1, 1), (33, 2, 11), (1024, 4, 2), (70, 8, 5)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_convolution_and_state_of_a_decode_step_in_one_launch(C, taps, groups, dtype):
+    """Four requests decode twelve tokens each, one token per request and step, after a prompt portion that went
+    through the kernels of any step; slots in another order than the requests."""
+    g = torch.Generator().manual_seed(C + taps)
+    w, nw = torch.randn(C, taps, generator=g) * 0.5, 1 + 0.3 * torch.randn(C, generator=g)
+    B, first, more = 4, [5, 1, 9, 2], 12
+    xs = [torch.randn(n + more, C, generator=g) * 2 for n in first]
+    normed = [pb.group_rms_norm(x.double(), nw.double(), groups, 1e-5) for x in xs]
+    want = [n + pb.causal_conv(n, w.double()) for n in normed]
+    state = torch.zeros(6, max((taps - 1) * C, 1), device=DEV)
+    slots = [4, 1, 0, 3]
+    got = [[] for _ in range(B)]
+    rows = torch.cat([x[:n] for x, n in zip(xs, first)]).to(DEV)
+    starts = [0]
+    for n in first:
+        starts.append(starts[-1] + n)
+    req = [i for i, n in enumerate(first) for _ in range(n)]
+    n32 = F().group_rmsnorm(rows, nw.to(DEV), groups, 1e-5, torch.float32)
+    out = F().causal_conv_residual(n32, w.to(DEV), state, 0, i32(starts), i32(req), i32(slots), dtype)
+    for i in range(B):
+        got[i].append(out[starts[i]:starts[i + 1]].cpu())
+    for step in range(more):
+        rows = torch.stack([xs[i][first[i] + step] for i in range(B)]).to(DEV)
+        out = F().norm_conv_decode(rows, nw.to(DEV), groups, 1e-5, w.to(DEV), state, 0, i32(list(range(B + 1))),
+                                   i32(slots), dtype)
+        for i in range(B):
+            got[i].append(out[i:i + 1].cpu())
+    tol = 3e-6 if dtype == torch.float32 else 8e-3
+    for i in range(B):
+        assert close(torch.cat(got[i]), want[i], tol), i
+    assert float(state[[2, 5]].abs().sum()) == 0.0 or taps == 1          # slots of no request are left alone
+
+
 # --------------------------------------------------------------------------- #
 # the two recurrences on the walk of the delta rule
 # --------------------------------------------------------------------------- #
