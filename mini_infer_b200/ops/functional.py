@@ -1270,7 +1270,7 @@ def norm_conv_decode(hidden: torch.Tensor, norm_weight: torch.Tensor, groups: in
     T, C = hidden.shape
     B = state_slot.numel()
     if T != B:
-        raise ValueError(f"norm_conv_decode: {T} rows for {B} requests (one token each is the contract)")
+        raise ValueError(f"norm_conv_decode: {T} rows for {B} requests (this kernel takes one token of each)")
     _chk(norm_weight, "norm_conv_decode norm weight", F32, (C,))
     _chk(w, "norm_conv_decode w", F32, (C, None))
     taps = w.shape[1]
