@@ -109,7 +109,16 @@ CONFIG_E = {
     ],
 }
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E}
+# delta layers only: a model that keeps no paged cache at all, only states
+CONFIG_F = {
+    "architecture": "Bogetar", "vocab": 77, "width": 36, "norm": {"eps": 1e-6, "groups": 2}, "canon": {"taps": 4},
+    "layers": [
+        _delta(3, 1, 12, 8, 2, _moe(20, 4, 2, 2.0, (2, 1))),
+        _delta(2, 2, 10, 14, 3, None),
+    ],
+}
+
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E, "F": CONFIG_F}
 
 
 def make_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:

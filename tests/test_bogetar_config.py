@@ -20,7 +20,7 @@ def test_the_architecture_is_registered():
     assert "Bogetar" in known_architectures()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_reader_and_description(name):
     cfg = bt.CONFIGS[name]
     c = BogetarConfig.from_json_dict(cfg)
@@ -66,7 +66,7 @@ def test_reader_and_description(name):
             assert ls.feed_forward_conv.get("tensor") == "canon2"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_manifest_matches_names_made_from_the_configuration(name):
     cfg = bt.CONFIGS[name]
     w = bt.make_weights(cfg, 1)

@@ -119,7 +119,7 @@ def run_and_check(runner, steps, cfg, w, reqs, dtype):
     return got, routing
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_every_cutting_against_the_plain_model(models, name, dtype):
     folder, cfg, w = models[name]
