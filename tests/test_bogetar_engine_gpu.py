@@ -72,20 +72,27 @@ def legitimate(idx, s, router, gap, what):
         assert float(kth - s[t, row].min()) <= gap, f"{what}: an expert below the last one it should choose"
 
 
-def reference(cfg, w, toks, routing, dtype, what=""):
-    """Plain logits under the engine's routing, after checking that every choice is a legitimate one."""
+def reference(cfg, w, toks, routing, dtype, what="", strict=True):
+    """Plain logits under the engine's routing, after checking that every choice is a legitimate one.  Without
+    ``strict`` (models of random shape in bfloat16, where a tiny router may sit on a knife's edge for many tokens)
+    the choices are taken as they are, and a position is allowed what 16-bit rounding alone does to the plain model
+    there."""
     forced = None
     if routing:
         forced = {li: torch.tensor([per[p] for p in range(len(toks))], dtype=torch.long) for li, per in routing.items()}
     rec = {}
     out = pb.forward(cfg, w, toks, rnd=ROUNDING[dtype], chosen=rec, forced=forced)
-    for li, (idx, s) in rec.items():
-        legitimate(idx, s, cfg["layers"][li]["mlp"]["router"], GAP[dtype], f"{what} layer {li}")
+    if strict:
+        for li, (idx, s) in rec.items():
+            legitimate(idx, s, cfg["layers"][li]["mlp"]["router"], GAP[dtype], f"{what} layer {li}")
     moved = None
+    chosen = {li: idx for li, (idx, _) in rec.items()}
     if dtype == "float32":
-        chosen = {li: idx for li, (idx, _) in rec.items()}
         low = pb.forward(cfg, w, toks, forced=chosen, dtype=torch.float32).double()
         moved = (low - out).abs().max(dim=1).values
+    elif not strict:
+        exact = pb.forward(cfg, w, toks, forced=chosen)
+        moved = (exact - out).abs().max(dim=1).values * 0.5
     return out, moved
 
 
@@ -104,16 +111,16 @@ def check(got, ref, tol):
 _references = {}
 
 
-def run_and_check(runner, steps, cfg, w, reqs, dtype):
+def run_and_check(runner, steps, cfg, w, reqs, dtype, strict=True):
     routing = {}
     got = run_trace(runner, steps, routing)
     ref = {}
     for rid in reqs:
         if any(k[0] == rid for k in got):
             # the plain model is slow: one run per (model, request, routing)
-            key = (id(w), dtype, tuple(reqs[rid]), json.dumps(routing.get(rid), sort_keys=True))
+            key = (id(w), dtype, strict, tuple(reqs[rid]), json.dumps(routing.get(rid), sort_keys=True))
             if key not in _references:
-                _references[key] = reference(cfg, w, reqs[rid], routing.get(rid), dtype, rid)
+                _references[key] = reference(cfg, w, reqs[rid], routing.get(rid), dtype, rid, strict)
             ref[rid] = _references[key]
     check(got, ref, TOL[dtype])
     return got, routing
