@@ -213,6 +213,7 @@ class SandwichResidual(Block):
         self._folded = {}
         self._ab = None
         self._ab_before = []
+        self._side_stream = None
 
     def tensor_decls(self) -> List[TensorDecl]:
         H = int(self.params["hidden_size"]) if self.scale_names else 0
@@ -274,10 +275,31 @@ class SandwichResidual(Block):
         if left is not None:
             hidden.add_(left)
         h = self._read(hidden, layer.mixer_norm, layer.mixer_conv if self.conv else None, ctx, caches.get("mixer_conv"))
-        y = layer.mixer.forward(h, ctx, caches.get("mixer"))
+        y2 = None
+        if (self.second and TUNING.parallel_residual_two_streams and h.is_cuda
+                and ctx.num_tokens <= TUNING.parallel_residual_two_streams_max_tokens_full_sm_mixer):
+            # The two mixers share nothing but the input they read: in steps of few tokens, whose kernels are short
+            # chains that leave the device idle, the second one goes to a second stream (decode at batch 8: 0.538 ->
+            # 0.456 ms and 1.117 -> 1.005 ms at the two bench sizes).  In a prompt step the walk of the recurrence
+            # beside the tensor-memory attention and the library's products, whose blocks want whole SMs, lost 7 to
+            # 19 %, so large steps stay on one stream.
+            main = torch.cuda.current_stream()
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=h.device)
+            side = self._side_stream
+            side.wait_stream(main)
+            h.record_stream(side)
+            with torch.cuda.stream(side):
+                y2 = layer.mixer_b.forward(h, ctx, caches.get("mixer_b"))
+            y2.record_stream(main)
+            y = layer.mixer.forward(h, ctx, caches.get("mixer"))
+            main.wait_stream(side)
+        else:
+            y = layer.mixer.forward(h, ctx, caches.get("mixer"))
+            if self.second:
+                y2 = layer.mixer_b.forward(h, ctx, caches.get("mixer_b"))
         if self.second:
             # a * y + b * y2 is formed inside the output norm's kernel, as a sum of rows with weights
-            y2 = layer.mixer_b.forward(h, ctx, caches.get("mixer_b"))
             wa, wb = self._weights(y.shape[0], y.device)
             y = WeightedRowSum(y, None, wa, y2, wb)
         elif self.a != 1.0:
