@@ -272,11 +272,20 @@ delta_prepare_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __r
 
 // The walk.  prep as delta_prepare_kernel leaves it; v heads at column v_col0 of qkv (H x dv).  out: [T, H*dv].
 // Without DELTA the write is the value itself, u = v_t (gated linear attention): S^T k_t is never formed.
+//
+// Segments (segs > 1; gated linear attention only, whose transition is diagonal): a request's portion is cut into
+// `segs` runs of seg_len tokens that are walked side by side, block z = request * segs + segment.  Segment 0 starts
+// from the request's state, the others from zero, and every segment leaves its final state in seg_state
+// [z][H][d][dv] instead of the slot.  The recurrence is linear in S, so what a later segment's read-outs lack is
+// (b_t * q_t)^T S_start with b_t the product of the decays since the segment's start: gla_segment_decay_kernel forms
+// b_t * q_t and the segments' whole decays, gla_segments_combine_kernel chains the final states into every
+// segment's true start state (and the request's new state), delta_segments_correct_kernel adds the missing term.
 template <int RP, bool DELTA>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, const float* __restrict__ prep,
                   float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
-                  const int* __restrict__ state_slot, float* __restrict__ out, int H, int d, int dv) {
+                  const int* __restrict__ state_slot, float* __restrict__ out, int H, int d, int dv,
+                  int segs, int seg_len, float* __restrict__ seg_state) {
     extern __shared__ __align__(16) float sm[];
     constexpr int DP = RP * kScanLanes;                 // rows, padded
     constexpr int MV = RP / 4;
@@ -285,11 +294,14 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, con
     constexpr int kBuf = kScanChunk * (ROW + kScanCols);
     float* os = sm + 2 * kBuf;                          // [chunk][16] results of the chunk
     wait_for_earlier_kernels();
-    const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * kScanCols;
+    const int z = blockIdx.z, b = segs > 1 ? z / segs : z, seg = segs > 1 ? z - b * segs : 0;
+    const int h = blockIdx.y, col0 = blockIdx.x * kScanCols;
     const int tid = threadIdx.x;
     const int r = tid & (kScanLanes - 1), lc = tid / kScanLanes, col = col0 + lc;
     const bool col_ok = col < dv;
-    const int q0 = q_start[b], n = q_start[b + 1] - q0;
+    const int qa = q_start[b], na = q_start[b + 1] - qa;
+    if (seg > 0 && seg * seg_len >= na) return;                 // a request shorter than its segments
+    const int q0 = qa + seg * seg_len, n = segs > 1 ? min(seg_len, na - seg * seg_len) : na;
     float* S = state + (int64_t)state_slot[b] * state_stride + (int64_t)h * d * dv;
     float s[RP];
 #pragma unroll
@@ -297,7 +309,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, con
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
             const int i = scan_row(r, m, x);
-            s[4 * m + x] = (col_ok && i < d) ? S[(int64_t)i * dv + col] : 0.f;
+            s[4 * m + x] = (seg == 0 && col_ok && i < d) ? S[(int64_t)i * dv + col] : 0.f;
         }
     const int64_t v_col = v_col0 + (int64_t)h * dv + col0;
     const int n_cols = min(kScanCols, dv - col0);
@@ -379,6 +391,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, con
             if (c < dv) out[(int64_t)(q0 + c0 + tt) * H * dv + (int64_t)h * dv + c] = os[idx];
         }
     }
+    if (segs > 1) S = seg_state + ((int64_t)z * H + h) * d * dv;       // the segment's final state, for the chain
 #pragma unroll
     for (int m = 0; m < MV; ++m)
 #pragma unroll
@@ -386,6 +399,128 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, con
             const int i = scan_row(r, m, x);
             if (col_ok && i < d) S[(int64_t)i * dv + col] = s[4 * m + x];
         }
+}
+
+// Gated linear attention walked in segments: for every token the query times the product of the decays since its
+// segment's start, qt[t][h][i] = q_t[i] * b_t[i] (what the start state must be read with), and per segment the whole
+// product bend[z][h][i].  A thread per (segment, head, key channel) multiplies its way through the segment.
+__global__ void __launch_bounds__(128)
+gla_segment_decay_kernel(const float* __restrict__ prep, const int* __restrict__ q_start, float* __restrict__ qt,
+                         float* __restrict__ bend, int H, int d, int DP, int segs, int seg_len) {
+    wait_for_earlier_kernels();
+    const int z = blockIdx.z, b = z / segs, seg = z - b * segs, h = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int qa = q_start[b], na = q_start[b + 1] - qa;
+    if (i >= d || seg * seg_len >= na) return;
+    const int n = min(seg_len, na - seg * seg_len);
+    const int ROW = 3 * DP + 4;
+    float acc = 1.f;
+    // eight tokens' decays and queries are asked for before the first product: the chain is the products alone
+    for (int t0 = 0; t0 < n; t0 += 8) {
+        float g[8], q[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int64_t tok = qa + seg * seg_len + min(t0 + u, n - 1);
+            const float* row = prep + (tok * H + h) * ROW;
+            g[u] = row[2 * DP + i];
+            q[u] = row[i];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (t0 + u < n) {
+                acc *= g[u];
+                qt[((int64_t)(qa + seg * seg_len + t0 + u) * H + h) * d + i] = q[u] * acc;
+            }
+        }
+    }
+    bend[((int64_t)z * H + h) * d + i] = acc;
+}
+
+// The segments' final states chained into every segment's true start state: with U_p the state segment p reached
+// from zero (segment 0: from the request's state) and b_p its whole decay per key channel, S_start[1] = U_0 and
+// S_start[p + 1] = diag(b_p) S_start[p] + U_p.  Element by element; S_start[p] replaces U_p in seg_state once U_p has
+// been read, and the state after the last segment goes to the request's slot.
+__global__ void __launch_bounds__(256)
+gla_segments_combine_kernel(float* __restrict__ seg_state, const float* __restrict__ bend, float* __restrict__ state,
+                            int64_t state_stride, const int* __restrict__ q_start, const int* __restrict__ state_slot,
+                            int H, int d, int dv, int segs, int seg_len) {
+    wait_for_earlier_kernels();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;           // element i * dv + c of the head's state
+    if (e >= d * dv) return;
+    const int i = e / dv;
+    const int na = q_start[b + 1] - q_start[b];
+    const int nseg = min(segs, (na + seg_len - 1) / seg_len);
+    float cur = seg_state[(((int64_t)b * segs) * H + h) * d * dv + e];
+    for (int p = 1; p < nseg; ++p) {
+        const int64_t zp = (int64_t)b * segs + p;
+        float* U = seg_state + (zp * H + h) * d * dv + e;
+        const float nxt = bend[(zp * H + h) * d + i] * cur + *U;
+        *U = cur;
+        cur = nxt;
+    }
+    state[(int64_t)state_slot[b] * state_stride + (int64_t)h * d * dv + e] = cur;
+}
+
+// out[t] += S_start[segment of t]^T qt[t] for the tokens of the segments behind the first.  A block takes 32 tokens
+// of one segment and 64 value columns of one head: the start state's slice in shared memory, a warp four tokens, a
+// lane two columns.
+constexpr int kCorrectTokens = 32, kCorrectCols = 64;
+__global__ void __launch_bounds__(256)
+delta_segments_correct_kernel(const float* __restrict__ seg_state, const float* __restrict__ qt, float* __restrict__ out,
+                              const int* __restrict__ q_start, int H, int d, int dv, int segs, int seg_len, int tiles,
+                              int col_chunks) {
+    extern __shared__ __align__(16) float corr_sm[];    // [d][64] start state, [8 warps][d][4 tokens] queries
+    wait_for_earlier_kernels();
+    const int b = blockIdx.z, h = blockIdx.y / col_chunks, cc = blockIdx.y % col_chunks;
+    const int p = 1 + blockIdx.x / tiles, tile = blockIdx.x % tiles;
+    const int qa = q_start[b], na = q_start[b + 1] - qa;
+    const int t_lo = p * seg_len + tile * kCorrectTokens;
+    const int t_hi = min(min(na, (p + 1) * seg_len), t_lo + kCorrectTokens);
+    if (t_lo >= t_hi) return;
+    const float* S0 = seg_state + (((int64_t)b * segs + p) * H + h) * d * dv;
+    const int c0 = cc * kCorrectCols;
+    float* Ssm = corr_sm;
+    float* qsm = corr_sm + d * kCorrectCols;
+    for (int idx = threadIdx.x; idx < d * kCorrectCols; idx += 256) {
+        const int i = idx / kCorrectCols, c = c0 + idx % kCorrectCols;
+        Ssm[idx] = c < dv ? S0[(int64_t)i * dv + c] : 0.f;
+    }
+    __syncthreads();
+    // a warp takes the tokens t_lo + warp, + 8, + 16, + 24 together: a number of the state is fetched once for four
+    // tokens, and the four queries' numbers of a row lie side by side in shared memory (one 16-byte load)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float4* qw = reinterpret_cast<float4*>(qsm) + warp * d;
+    for (int j = lane; j < d; j += 32) {
+        float q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int t = t_lo + warp + 8 * u;
+            q[u] = t < t_hi ? qt[((int64_t)(qa + t) * H + h) * d + j] : 0.f;
+        }
+        qw[j] = make_float4(q[0], q[1], q[2], q[3]);
+    }
+    __syncwarp();
+    float a[4][2];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) a[u][0] = a[u][1] = 0.f;
+    for (int j = 0; j < d; ++j) {
+        const float4 q4 = qw[j];
+        const float s0 = Ssm[j * kCorrectCols + lane], s1 = Ssm[j * kCorrectCols + 32 + lane];
+        a[0][0] += q4.x * s0; a[0][1] += q4.x * s1;
+        a[1][0] += q4.y * s0; a[1][1] += q4.y * s1;
+        a[2][0] += q4.z * s0; a[2][1] += q4.z * s1;
+        a[3][0] += q4.w * s0; a[3][1] += q4.w * s1;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int t = t_lo + warp + 8 * u;
+        if (t < t_hi) {
+            float* orow = out + ((int64_t)(qa + t) * H + h) * dv + c0;
+            if (c0 + lane < dv) orow[lane] += a[u][0];
+            if (c0 + 32 + lane < dv) orow[32 + lane] += a[u][1];
+        }
+    }
 }
 
 // xbc: [T, ld_x] float after the convolution: x heads at column 0 (H x P), B groups at H*P (G x N), C groups
@@ -687,12 +822,11 @@ int mi_norm_conv_decode(const float* hidden, const float* norm_w, int groups, fl
 // floats of one (token, head) of the scratch that mi_delta_scan needs: T * H * this many
 int mi_delta_scan_prep_row(int d) { return 3 * (d <= 64 ? 64 : (d <= 128 ? 128 : 256)) + 4; }
 
-// form: see delta_prepare_kernel (0 and 1: the delta rule; 2: gated linear attention, which reads neither
-// beta_raw nor a_log); tau: form 2 only
-int mi_delta_scan_form(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
-                       const float* a_log, const float* dt_bias, float* state, int64_t state_stride,
-                       const int* q_start, const int* state_slot, float* out, float* prep, int T, int B, int H, int G,
-                       int d, int dv, float q_scale, int form, float tau, cudaStream_t stream) {
+static int delta_scan_launch(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
+                             const float* a_log, const float* dt_bias, float* state, int64_t state_stride,
+                             const int* q_start, const int* state_slot, float* out, float* prep, int T, int B, int H, int G,
+                             int d, int dv, float q_scale, int form, float tau, int segs, int seg_len, float* seg_state,
+                             float* qt, float* bend, cudaStream_t stream) {
     if (B <= 0 || T <= 0) return kOk;
     if (d < 1 || d > 256 || dv < 1) { set_last_error("delta rule: key size %d outside [1, 256] or value size %d", d, dv); return kBadShape; }
     if (G < 1 || H % G) { set_last_error("delta rule: %d heads are not a multiple of %d key heads", H, G); return kBadShape; }
@@ -702,23 +836,66 @@ int mi_delta_scan_form(const float* qkv, int ld_qkv, const float* beta_raw, int 
         set_last_error("delta rule: form %d with tau %g, or a form that lacks its write strengths or decay rates", form, (double)tau);
         return kBadShape;
     }
+    if (segs < 1 || (segs > 1 && (form != kSigmoidDecay || seg_len < 1 || !seg_state || !qt || !bend ||
+                                  (int64_t)B * segs > 65535 || (int64_t)H * ((dv + kCorrectCols - 1) / kCorrectCols) > 65535))) {
+        set_last_error("walk in segments: %d segments of %d tokens for %d requests (gated linear attention only, with its scratch)",
+                       segs, seg_len, B);
+        return kBadShape;
+    }
     const int DP = d <= 64 ? 64 : (d <= 128 ? 128 : 256);
     launch_dependent(delta_prepare_kernel, dim3(T, H), dim3(128), 0, stream, qkv, ld_qkv, beta_raw, ld_beta, a_raw, ld_a,
                      a_log, dt_bias, prep, H, G, d, DP, q_scale, form, tau);
-    const dim3 grid((dv + kScanCols - 1) / kScanCols, H, B);
+    if (segs > 1)
+        launch_dependent(gla_segment_decay_kernel, dim3((d + 127) / 128, H, B * segs), dim3(128), 0, stream,
+                         (const float*)prep, q_start, qt, bend, H, d, DP, segs, seg_len);
+    const dim3 grid((dv + kScanCols - 1) / kScanCols, H, B * segs);
     MI_SCAN_DISPATCH(d, {
         const size_t smem = sizeof(float) * (2 * kScanChunk * (3 * RP * kScanLanes + 4 + kScanCols) + kScanChunk * kScanCols);
         if (form == kSigmoidDecay) {
             cudaFuncSetAttribute(delta_scan_kernel<RP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             launch_dependent(delta_scan_kernel<RP, false>, grid, dim3(128), smem, stream, qkv, ld_qkv, (int64_t)2 * G * d,
-                             (const float*)prep, state, state_stride, q_start, state_slot, out, H, d, dv);
+                             (const float*)prep, state, state_stride, q_start, state_slot, out, H, d, dv, segs, seg_len,
+                             seg_state);
         } else {
             cudaFuncSetAttribute(delta_scan_kernel<RP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             launch_dependent(delta_scan_kernel<RP, true>, grid, dim3(128), smem, stream, qkv, ld_qkv, (int64_t)2 * G * d,
-                             (const float*)prep, state, state_stride, q_start, state_slot, out, H, d, dv);
+                             (const float*)prep, state, state_stride, q_start, state_slot, out, H, d, dv, 1, 0,
+                             (float*)nullptr);
         }
     });
-    return finish_launch("delta_scan", 2);
+    if (segs == 1) return finish_launch("delta_scan", 2);
+    launch_dependent(gla_segments_combine_kernel, dim3((d * dv + 255) / 256, H, B), dim3(256), 0, stream, seg_state,
+                     (const float*)bend, state, state_stride, q_start, state_slot, H, d, dv, segs, seg_len);
+    const int tiles = (seg_len + kCorrectTokens - 1) / kCorrectTokens, chunks = (dv + kCorrectCols - 1) / kCorrectCols;
+    const size_t corr_smem = sizeof(float) * ((size_t)d * kCorrectCols + 8 * 4 * d);
+    cudaFuncSetAttribute(delta_segments_correct_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)corr_smem);
+    launch_dependent(delta_segments_correct_kernel, dim3((segs - 1) * tiles, H * chunks, B), dim3(256), corr_smem, stream,
+                     (const float*)seg_state, (const float*)qt, out, q_start, H, d, dv, segs, seg_len, tiles, chunks);
+    return finish_launch("delta_scan", 5);
+}
+
+// form: see delta_prepare_kernel (0 and 1: the delta rule; 2: gated linear attention, which reads neither
+// beta_raw nor a_log); tau: form 2 only
+int mi_delta_scan_form(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
+                       const float* a_log, const float* dt_bias, float* state, int64_t state_stride,
+                       const int* q_start, const int* state_slot, float* out, float* prep, int T, int B, int H, int G,
+                       int d, int dv, float q_scale, int form, float tau, cudaStream_t stream) {
+    return delta_scan_launch(qkv, ld_qkv, beta_raw, ld_beta, a_raw, ld_a, a_log, dt_bias, state, state_stride, q_start,
+                             state_slot, out, prep, T, B, H, G, d, dv, q_scale, form, tau, 1, 0, nullptr, nullptr, nullptr,
+                             stream);
+}
+
+// Gated linear attention (form 2) with every request's portion walked as `segs` segments of seg_len tokens side by
+// side (see delta_scan_kernel): seg_state holds B * segs * H * d * dv floats, qt T * H * d, bend B * segs * H * d.
+// The sums of a token then run in another order than in the walk of one piece: the two agree within rounding, not
+// bit for bit.
+int mi_gla_scan_segments(const float* qkv, int ld_qkv, const float* a_raw, int ld_a, const float* dt_bias, float* state,
+                         int64_t state_stride, const int* q_start, const int* state_slot, float* out, float* prep, int T,
+                         int B, int H, int d, int dv, float q_scale, float tau, int segs, int seg_len, float* seg_state,
+                         float* qt, float* bend, cudaStream_t stream) {
+    return delta_scan_launch(qkv, ld_qkv, nullptr, 0, a_raw, ld_a, nullptr, dt_bias, state, state_stride, q_start,
+                             state_slot, out, prep, T, B, H, H, d, dv, q_scale, kSigmoidDecay, tau, segs, seg_len, seg_state,
+                             qt, bend, stream);
 }
 
 int mi_delta_scan(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,

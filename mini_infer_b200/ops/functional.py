@@ -1292,16 +1292,35 @@ def norm_conv_decode(hidden: torch.Tensor, norm_weight: torch.Tensor, groups: in
 DELTA_FORMS = {"channel_decay": 0, "head_decay": 1, "sigmoid_decay": 2}
 
 
+def scan_segments(max_q_len: int, min_tokens: int, segment_tokens: int, max_segments: int) -> Tuple[int, int]:
+    """``(segments, tokens per segment)`` for a step whose longest portion has ``max_q_len`` tokens: one segment
+    below ``min_tokens``; else runs of about ``segment_tokens`` tokens (whole chunks of 16), at most
+    ``max_segments`` of them."""
+    if max_q_len < max(min_tokens, 2):
+        return 1, 0
+    segs = max(2, min(max_segments, -(-max_q_len // segment_tokens)))
+    per = -(-max_q_len // segs)
+    per = -(-per // 16) * 16
+    return -(-max_q_len // per), per
+
+
 def delta_scan(qkv: torch.Tensor, beta_raw: Optional[torch.Tensor], beta_col: int, a_raw: torch.Tensor, a_col: int,
                a_log: Optional[torch.Tensor], dt_bias: torch.Tensor, state: torch.Tensor, state_offset: int,
                q_start: torch.Tensor, state_slot: torch.Tensor, heads: int, key_heads: int, d: int, dv: int,
-               q_scale: float, form: str = "channel_decay", tau: float = 1.0) -> torch.Tensor:
+               q_scale: float, form: str = "channel_decay", tau: float = 1.0, segments: int = 1,
+               segment_tokens: int = 0) -> torch.Tensor:
     """Gated delta rule with a decay per head and key channel, token by token over every request's portion.
 
     ``form`` ``head_decay``: ONE decay per head (``a_raw`` holds ``heads`` columns and ``dt_bias`` ``heads``
     numbers).  ``form`` ``sigmoid_decay``: gated linear attention, ``S <- diag(g) S + k v^T; o = S^T q`` with
     q (times ``q_scale``) and k as they are and ``g = sigmoid(a + dt_bias)^(1 / tau)`` per head and key channel;
     ``beta_raw`` and ``a_log`` are not read.
+
+    ``segments`` > 1 (``sigmoid_decay`` only, whose transition is diagonal): every request's portion is cut into that
+    many runs of ``segment_tokens`` tokens which are walked side by side from zero; the runs' final states are then
+    chained into every run's true start state and the read-outs corrected by ``(b_t q_t)^T S_start`` with ``b_t`` the
+    product of the decays since the run's start.  The chain of dependent steps is a run's length, not the portion's;
+    the sums of a token run in another order than in one piece, so the two agree within rounding, not bit for bit.
 
     ``qkv`` float32 ``[T, 2*key_heads*d + heads*dv]`` (q | k | v after their convolutions; the rows may go on
     with columns that are not read); ``beta_raw`` holds
@@ -1335,6 +1354,19 @@ def delta_scan(qkv: torch.Tensor, beta_raw: Optional[torch.Tensor], beta_col: in
     out = torch.empty(T, heads * dv, dtype=F32, device=qkv.device)
     # unit vectors, decays and write strengths of all tokens, made ready by a kernel before the walk
     prep = torch.empty(T * heads * library().mi_delta_scan_prep_row(d), dtype=F32, device=qkv.device)
+    if segments > 1:
+        if form != "sigmoid_decay" or segment_tokens < 1 or B * segments > 65535:
+            raise ValueError(f"delta_scan: {segments} segments of {segment_tokens} tokens for {B} requests in the form "
+                             f"'{form}' (segments are built for 'sigmoid_decay')")
+        seg_state = torch.empty(B * segments * heads * d * dv, dtype=F32, device=qkv.device)
+        qt = torch.empty(T * heads * d, dtype=F32, device=qkv.device)
+        bend = torch.empty(B * segments * heads * d, dtype=F32, device=qkv.device)
+        check(library().mi_gla_scan_segments(
+            _ptr(qkv), qkv.shape[1], a_raw.data_ptr() + 4 * a_col, a_raw.shape[1], _ptr(dt_bias),
+            state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start), _ptr(state_slot), _ptr(out), _ptr(prep), T,
+            B, heads, d, dv, float(q_scale), float(tau), int(segments), int(segment_tokens), _ptr(seg_state), _ptr(qt),
+            _ptr(bend), _stream()), "delta_scan")
+        return out
     if form == "channel_decay":
         check(library().mi_delta_scan(_ptr(qkv), qkv.shape[1], beta_raw.data_ptr() + 4 * beta_col, beta_raw.shape[1],
                                       a_raw.data_ptr() + 4 * a_col, a_raw.shape[1], _ptr(a_log), _ptr(dt_bias),

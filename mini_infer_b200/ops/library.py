@@ -72,6 +72,7 @@ _SIGNATURES = {
     "mi_causal_conv_residual": [P, I, P, I, P, L, P, P, P, P, I, I, I, I, I, I, P],
     "mi_norm_conv_decode": [P, P, I, F, P, P, L, P, P, P, I, I, I, I, P],
     "mi_delta_scan_form": [P, I, P, I, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, I, F, P],
+    "mi_gla_scan_segments": [P, I, P, I, P, P, L, P, P, P, P, I, I, I, I, I, F, F, I, I, P, P, P, P],
     "mi_attn_mix_form": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, P, P],
     "mi_attn_mix_tc_form": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, I, P, P],
     "mi_attn_prefill_tc_logistic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],

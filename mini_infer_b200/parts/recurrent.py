@@ -37,6 +37,7 @@ import torch
 from ..config.registry import register_part
 from ..ops import functional as F
 from .base import CacheBinding, Mixer, Runtime, StateNeed, StepContext, TensorDecl, linear
+from .tuning import TUNING
 
 
 def _f32(t: torch.Tensor, dev) -> torch.Tensor:
@@ -325,8 +326,13 @@ class GatedLinearAttention(Mixer):
         state = ctx.states[cache.group]
         proj = linear(x, self.w_in, torch.float32)                       # q | k | v | gate
         z = linear(linear(x, self.w_a1, self.rt.act), self.w_a2, torch.float32)
+        # long portions of the bfloat16 path are walked in segments side by side; the float32 path keeps one walk for
+        # every step, so that its sums run in one order however a prompt was cut
+        segs, per = (1, 0) if self.rt.act != torch.bfloat16 else F.scan_segments(
+            ctx.max_q_len, TUNING.scan_segments_min_tokens, TUNING.scan_segment_tokens, TUNING.scan_max_segments)
         o = F.delta_scan(proj, None, 0, z, 0, None, self.b_a2, state, 0, ctx.q_start, ctx.state_slot, self.nh,
-                         self.nh, self.d, self.dv, self.d ** -0.5, form="sigmoid_decay", tau=self.tau)
+                         self.nh, self.d, self.dv, self.d ** -0.5, form="sigmoid_decay", tau=self.tau,
+                         segments=segs, segment_tokens=per)
         y = F.gated_group_rmsnorm(o, proj, 2 * self.n_qk + self.n_v, self.norm_w, self.nh, False, self.eps,
                                   self.rt.act, silu_after=True)
         return linear(y, self.w_o, torch.float32)

@@ -96,6 +96,15 @@ class Tuning:
     # A block whose mixer and feed-forward read the same residual (``parallel_residual``) runs the feed-forward on
     # a second stream beside the mixer: a recurrent mixer walks a prompt with a few warps per SM and the
     # feed-forward's products fill the rest; in a decode step the two chains of small kernels run side by side.
+    # The walk of gated linear attention (bfloat16 path): a portion of at least ``scan_segments_min_tokens`` tokens is
+    # cut into segments of about ``scan_segment_tokens`` tokens (at most ``scan_max_segments`` of them) that are walked
+    # side by side and chained afterwards, which shortens the chain of dependent steps from the portion's length to a
+    # segment's.  (The float32 path walks every portion in one piece: its sums run in one order however a prompt is
+    # cut.  The delta rule's transition is a full matrix, not a diagonal: chaining it cost more than it saved.)
+    scan_segments_min_tokens: int = 256
+    scan_segment_tokens: int = 128
+    scan_max_segments: int = 32
+
     parallel_residual_two_streams: bool = True
     # ... unless the mixer's kernels of a large step want whole SMs themselves (tensor-memory attention: its
     # blocks and those of the feed-forward's tensor-core products cannot sit on one SM, and a block that

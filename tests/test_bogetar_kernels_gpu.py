@@ -164,15 +164,18 @@ def plain_delta(q, k, v, beta, decay):
     return torch.stack(out), S
 
 
-def walk(form, qkv, beta, a, a_log, bias, H, G, d, dv, scale, cuts, tau=1.0, slot=1):
+def walk(form, qkv, beta, a, a_log, bias, H, G, d, dv, scale, cuts, tau=1.0, slot=1, segment_tokens=0):
+    """``segment_tokens``: portions longer than that are walked in segments of so many tokens side by side."""
     T = qkv.shape[0]
     state = torch.randn(3, H * d * dv + 5, generator=torch.Generator().manual_seed(1)).to(DEV)
     state[slot, :H * d * dv] = 0.0
     outs, lo = [], 0
     for n in cuts:
+        segs = -(-n // segment_tokens) if segment_tokens and n > segment_tokens else 1
         outs.append(F().delta_scan(qkv[lo:lo + n].to(DEV).contiguous(), None if beta is None else beta[lo:lo + n].to(DEV).contiguous(),
                                    0, a[lo:lo + n].to(DEV).contiguous(), 0, None if a_log is None else a_log.to(DEV),
-                                   bias.to(DEV), state, 0, i32([0, n]), i32([slot]), H, G, d, dv, scale, form=form, tau=tau))
+                                   bias.to(DEV), state, 0, i32([0, n]), i32([slot]), H, G, d, dv, scale, form=form, tau=tau,
+                                   segments=segs, segment_tokens=segment_tokens if segs > 1 else 0))
         lo += n
     assert lo == T
     return torch.cat(outs).cpu(), state[slot, :H * d * dv].cpu().view(H, d, dv)
@@ -209,10 +212,11 @@ def test_gated_linear_attention_on_the_same_walk(H, d, dv, tau):
     v = x[:, 2 * H * d:2 * H * d + H * dv].view(T, H, dv)
     decay = (pb.sigmoid(z.double() + bias.double()) ** (1.0 / tau)).view(T, H, d)
     want, S = plain_delta(q, k, v, None, decay)
-    for cuts in ([T], [1] * T, [7, 2, 1, 16, 17, 2]):
-        got, state = walk("sigmoid_decay", qkv, None, z, None, bias, H, H, d, dv, d ** -0.5, cuts, tau=tau)
-        assert close(got.view(T, H, dv), want, 2e-5), cuts
-        assert close(state, S, 2e-5), cuts
+    for cuts, seg in (([T], 0), ([1] * T, 0), ([7, 2, 1, 16, 17, 2], 0), ([T], 16), ([T], 7), ([20, 25], 9), ([T], 44)):
+        got, state = walk("sigmoid_decay", qkv, None, z, None, bias, H, H, d, dv, d ** -0.5, cuts, tau=tau,
+                          segment_tokens=seg)
+        assert close(got.view(T, H, dv), want, 2e-5), (cuts, seg)
+        assert close(state, S, 2e-5), (cuts, seg)
 
 
 @pytest.mark.parametrize("form", ["head_decay", "sigmoid_decay"])
@@ -247,10 +251,46 @@ def test_a_far_write_is_read_back_after_hundreds_of_tokens(form):
         args = (None, z, None, bias)
         scale, tau = 1.0, 2.0
     assert float(want[T - 1].abs().max()) > 0.3                    # the far value is what the last read-out is made of
-    for cuts in ([T], [300] + [1] * 120, [5, 2, 200] + [1] * 100 + [113]):
-        got, _ = walk(form, qkv, args[0], args[1], args[2], args[3], H, H, d, dv, scale, cuts, tau=tau)
-        assert close(got.view(T, H, dv)[T - 1], want[T - 1], 5e-5), cuts
-        assert close(got.view(T, H, dv), want, 5e-5), cuts
+    runs = [([T], 0), ([300] + [1] * 120, 0), ([5, 2, 200] + [1] * 100 + [113], 0)]
+    if form == "sigmoid_decay":
+        runs += [([T], 64), ([300] + [1] * 120, 32)]                 # long portions walked in segments side by side
+    for cuts, seg in runs:
+        got, _ = walk(form, qkv, args[0], args[1], args[2], args[3], H, H, d, dv, scale, cuts, tau=tau, segment_tokens=seg)
+        assert close(got.view(T, H, dv)[T - 1], want[T - 1], 5e-5), (cuts, seg)
+        assert close(got.view(T, H, dv), want, 5e-5), (cuts, seg)
+
+
+def test_unequal_requests_walked_in_segments_side_by_side():
+    """Gated linear attention of three requests in one step, one of a single token, one shorter than a segment and
+    one of many segments, in slots that hold states from before."""
+    H, d, dv, seg = 3, 24, 40, 32
+    g = torch.Generator().manual_seed(8)
+    lens = [1, 20, 150]
+    T = sum(lens)
+    qkv = torch.randn(T, 2 * H * d + H * dv, generator=g)
+    a, bias = torch.randn(T, H * d, generator=g), torch.randn(H * d, generator=g) + 1
+    state0 = torch.randn(4, H * d * dv, generator=g) * 0.3
+    slots = [2, 0, 3]
+    x = qkv.double()
+    state = state0.clone().to(DEV)
+    got = F().delta_scan(qkv.to(DEV), None, 0, a.to(DEV), 0, None, bias.to(DEV), state, 0, i32([0, 1, 21, T]), i32(slots),
+                         H, H, d, dv, d ** -0.5, form="sigmoid_decay", tau=4.0, segments=-(-150 // seg),
+                         segment_tokens=seg).cpu().view(T, H, dv)
+    lo = 0
+    for n, slot in zip(lens, slots):
+        rows = x[lo:lo + n]
+        q, k = rows[:, :H * d].view(n, H, d) * d ** -0.5, rows[:, H * d:2 * H * d].view(n, H, d)
+        v = rows[:, 2 * H * d:].view(n, H, dv)
+        decay = (pb.sigmoid(a[lo:lo + n].double() + bias.double()) ** 0.25).view(n, H, d)
+        S = state0[slot].double().view(H, d, dv).clone()
+        out = []
+        for t in range(n):
+            S = decay[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+            out.append(torch.einsum("hkv,hk->hv", S, q[t]))
+        assert close(got[lo:lo + n], torch.stack(out), 3e-5), n
+        assert close(state[slot].cpu().view(H, d, dv), S, 3e-5), n
+        lo += n
+    assert torch.equal(state[1].cpu(), state0[1])          # a slot of no request is left alone
 
 
 @pytest.mark.parametrize("heads,dv", [(4, 10), (2, 64), (3, 33), (1, 128)])
