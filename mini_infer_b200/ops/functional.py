@@ -399,7 +399,7 @@ def prefill_attention_tc_logistic(q: torch.Tensor, k_cache: torch.Tensor, v_cach
                                   block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor,
                                   max_q_len: int, window: int, scale: float, head_bias: torch.Tensor) -> torch.Tensor:
     """The tcgen05 attention without a softmax: a visible key's weight is ``logistic(score * scale +
-    head_bias[h])`` by itself, not normalised over the keys (the contract of :func:`attention_mix` with
+    head_bias[h])`` by itself, not normalised over the keys (what :func:`attention_mix` computes with
     ``head_bias``).  bfloat16; key and value heads of 64 or 128 numbers each, not necessarily alike.  Returns
     ``[T, nh, dv]``.  Call :func:`check_tc_status` after the step."""
     global _tc_pending
