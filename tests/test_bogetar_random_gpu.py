@@ -9,7 +9,8 @@ import torch
 
 import bogetar_tiny as bt
 import traces
-from test_bogetar_engine_gpu import run_and_check, runner_for
+from engine_harness import run_trace
+from test_bogetar_engine_gpu import TOL, reference, run_and_check, runner_for
 
 pytestmark = pytest.mark.gpu
 
@@ -72,3 +73,49 @@ def test_models_of_random_shape_in_several_cuttings(seed, tmp_path):
                       traces.mixed(reqs, max_live=3, seed=seed, decode_tail=9)):
             run_and_check(runner, steps, cfg, w, reqs, dtype, strict=dtype == "float32")
             assert runner.cache.used_pages() == [0] * len(runner.cache.pools)
+
+
+MEDIUM = {
+    "architecture": "Bogetar", "vocab": 512, "width": 256, "norm": {"eps": 1e-6, "groups": 2}, "canon": {"taps": 4},
+    "layers": [
+        bt._parallel(bt._left(8, 2, 64, 128, 200, 0.11, {"base": 20000.0, "dims": 32}), bt._right(4, 32, 64, 16.0, 16), 0.6, 0.9,
+                     bt._moe(128, 16, 4, 2.0, (4, 3))),
+        bt._delta(4, 2, 64, 64, 4, bt._moe(128, 16, 4, 2.0, (4, 3))),
+        bt._parallel(bt._left(4, 4, 128, 128, 300, 0.08, {"base": 20000.0, "dims": 128}), bt._right(8, 16, 32, 8.0, 8), 0.7, 0.8,
+                     bt._moe(64, 8, 2, 3.0, (2, 1))),
+        bt._delta(8, 8, 32, 128, 3, None),
+        bt._parallel(bt._left(6, 3, 128, 64, 64, 0.08, None), bt._right(2, 64, 64, 4.0, 4), 1.0, 1.0, bt._moe(128, 4, 1, 2.0)),
+    ],
+}
+
+
+def test_a_model_of_middling_size_with_long_prompts(tmp_path):
+    """Sizes that every tensor-core kernel of the bfloat16 path takes (the tensor-memory attention with key and value
+    heads alike and not, the tensor-core expert products), prompts long enough for windows to pass, for pages to be
+    given back and for linear attention to be walked in segments.  float32: every position strictly.  bfloat16: a
+    head's very first read-out is a multiple of ONE vector that is then normalised, so its sign hangs on the sign of
+    one dot product, and where that lies near zero 16-bit rounding may turn it: nearly all positions must agree,
+    not all."""
+    cfg = MEDIUM
+    w = bt.make_weights(cfg, seed=5)
+    folder = bt.write_folder(str(tmp_path / "m"), cfg, w)
+    reqs = bt.random_requests(cfg, [700, 3, 290, 41], seed=3)
+    args = dict(page_size=16, max_requests=4, num_pages=160, max_tokens_per_step=1200, max_context=1200)
+    cuttings = (traces.whole(reqs), traces.tail_decoded(reqs, tail=40), traces.portions(reqs, (257, 2, 300, 7, 64, 31)),
+                traces.mixed(reqs, max_live=4, seed=1, decode_tail=12))
+    runner = runner_for(folder, "float32", **args)
+    for steps in cuttings:
+        run_and_check(runner, steps, cfg, w, reqs, "float32")
+    runner = runner_for(folder, "bfloat16", **args)
+    assert all(l.parts["mixer"]._logistic_tc for l in runner.model.layers if "mixer_b" in l.parts)
+    assert all(l.parts["feed_forward"]._tc for l in runner.model.layers if "feed_forward" in l.parts)
+    for steps in cuttings:
+        routing = {}
+        got = run_trace(runner, steps, routing)
+        ref = {rid: reference(cfg, w, reqs[rid], routing.get(rid), "bfloat16", rid, strict=False)[0] for rid in reqs}
+        bad = 0
+        for (rid, pos), row in got.items():
+            assert bool(torch.isfinite(row).all())
+            scale = float(ref[rid].abs().max())
+            bad += float((row.double() - ref[rid][pos]).abs().max()) / scale > TOL["bfloat16"]
+        assert bad <= 0.03 * len(got), f"{bad} of {len(got)} positions apart"
